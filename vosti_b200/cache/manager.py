@@ -129,8 +129,8 @@ class CacheManager:
                     # zeros, not empty: the decode kernel reads whole boxes of 16 keys and masks
                     # afterwards, so slots nobody wrote yet must hold finite values
                     cache.tensors = tuple(
-                        torch.zeros((num_pages, spec.heads, page_size, spec.width), dtype=dtype, device=device)
-                        for _ in range(spec.entries))
+                        torch.zeros((num_pages, spec.heads, page_size, width), dtype=dtype, device=device)
+                        for width in spec.entry_widths())
             self.layer_caches.append(cache)
         for layer, spec in enumerate(state_specs):
             if spec is not None and device is not None:

@@ -72,10 +72,16 @@ class LayerSpec:
 class RunEntry:
     """One entry of the run order: run ``layer``; if ``cache_from`` is set the
     layer's mixer reads the cache (or state) that layer wrote instead of
-    keeping one of its own."""
+    keeping one of its own. A layer that runs several times with caches of its own
+    (a loop over a span of layers) numbers its runs with ``instance``: every
+    (layer, instance) pair owns a cache and a state. ``reenter`` marks the entry at
+    which a pass of such a loop begins: the model's re-entry part (`ModelSpec.reentry`)
+    transforms the residual stream right before this layer runs."""
 
     layer: int
     cache_from: Optional[int] = None
+    instance: int = 0
+    reenter: bool = False
 
 
 @dataclass(frozen=True)
@@ -94,6 +100,8 @@ class ModelSpec:
     layer_prefix: str = "model.layers.{i}."
     embedding: PartSpec = PartSpec("table")      # token ids -> hidden rows (parameter: scale)
     head: PartSpec = PartSpec("linear")          # hidden rows -> logits (parameters: bias, scale, softcap)
+    reentry: Optional[PartSpec] = None           # what a run entry with `reenter` does to the stream
+    reentry_name: str = "loop.in"                # its `weight` tensor in the checkpoint
     extra: Mapping[str, Any] = field(default_factory=dict)
 
     def validate(self) -> None:
@@ -109,3 +117,10 @@ class ModelSpec:
                 if not 0 <= entry.cache_from < len(self.layers):
                     raise ConfigError(f"run order reads cache of layer {entry.cache_from}, "
                                       f"model has {len(self.layers)}")
+            if entry.instance < 0:
+                raise ConfigError("run order: a layer's runs are numbered from 0")
+            if entry.reenter and self.reentry is None:
+                raise ConfigError("run order marks a re-entry but the model names no re-entry part")
+        owned = [(e.layer, e.instance) for e in self.run_order if e.cache_from is None]
+        if len(set(owned)) != len(owned):
+            raise ConfigError("run order: two runs of a layer own the same cache; number them with `instance`")

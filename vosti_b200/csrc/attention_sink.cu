@@ -1,0 +1,187 @@
+// Paged causal attention without rotation, with three optional additions, and key and value
+// heads of different widths:
+//   * a query temperature: the query at position p is multiplied by
+//     1 + coef * ln(floor((p + 1) / every) + 1);
+//   * a learned bias per (distance, head) added to the scaled score. The host hands a table
+//     bias[head][min(distance, last)] (already in base-2 units): beyond `last` the bias no
+//     longer changes, so the table is as long as the distances that differ;
+//   * a sink: one more term exp(sink[head]) in the softmax denominator, with no key or value.
+//
+// Two kernels: the projection's post-pass (temperature, keys and values into their cache
+// slots) and the attention itself on the CUDA cores, one warp per (query token, query head),
+// float32 arithmetic for both storage types. A tile is 32 keys aligned to the absolute key
+// index, so a row's order of arithmetic depends on its position only, not on how the prompt
+// was cut or what else is in the batch.
+#include "common.cuh"
+
+namespace {
+constexpr int WARPS = 4;
+constexpr int MAX_W = 256;          // widest key or value head
+constexpr float LOG2E = 1.4426950408889634f;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                 const int* __restrict__ positions, const int* __restrict__ slot_mapping, int64_t num_slots,
+                 int page_size, int nq, int nkv, int dk, int dv, float temp_coef, int temp_every, unsigned* status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int wq = nq * dk, wk = nkv * dk, wv = nkv * dv;
+  const T* row = qkv + (int64_t)t * (wq + wk + wv);
+  float temp = 1.f;
+  if (temp_coef != 0.f) temp = 1.f + temp_coef * logf((float)((positions[t] + 1) / temp_every + 1));
+  for (int i = threadIdx.x; i < wq; i += blockDim.x) q_out[(int64_t)t * wq + i] = from_f32<T>(to_f32(row[i]) * temp);
+  if (k_cache == nullptr) return;
+  const int64_t slot = slot_mapping[t];
+  if (slot < 0 || slot >= num_slots) {
+    if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_SLOT_RANGE);
+    return;
+  }
+  const int64_t page = slot / page_size, offset = slot % page_size;
+  for (int i = threadIdx.x; i < wk; i += blockDim.x) {
+    const int g = i / dk, c = i % dk;
+    k_cache[((page * nkv + g) * page_size + offset) * dk + c] = row[wq + i];
+  }
+  for (int i = threadIdx.x; i < wv; i += blockDim.x) {
+    const int g = i / dv, c = i % dv;
+    v_cache[((page * nkv + g) * page_size + offset) * dv + c] = row[wq + wk + i];
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                      T* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ request_of,
+                      const int* __restrict__ block_table, int max_pages, int page_size, int num_pages, int tokens,
+                      int nq, int nkv, int dk, int dv, float scale_log2, int window, const float* __restrict__ bias,
+                      int bias_last, const float* __restrict__ sink, unsigned* status) {
+  extern __shared__ float q_smem[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t wid = (int64_t)blockIdx.x * WARPS + warp;
+  if (wid >= (int64_t)tokens * nq) return;
+  const int t = (int)(wid / nq), h = (int)(wid % nq);
+  const int g = h / (nq / nkv);
+  float* qs = q_smem + warp * dk;
+  const T* qrow = q + ((int64_t)t * nq + h) * dk;
+  for (int i = lane; i < dk; i += 32) qs[i] = to_f32(qrow[i]);
+  __syncwarp();
+
+  const int b = request_of[t];
+  const int pos = positions[t];
+  const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int* table = block_table + (int64_t)b * max_pages;
+  const float* bias_h = bias != nullptr ? bias + (int64_t)h * (bias_last + 1) : nullptr;
+
+  float m = -INFINITY, l = 0.f;
+  float acc[MAX_W / 32];
+#pragma unroll
+  for (int i = 0; i < MAX_W / 32; ++i) acc[i] = 0.f;
+
+  for (int j0 = (kstart / 32) * 32; j0 <= pos; j0 += 32) {
+    const int j = j0 + lane;
+    bool valid = j >= kstart && j <= pos;
+    int64_t slot = 0;
+    float s = -INFINITY;
+    if (valid) {
+      const int slot_in_table = j / page_size;
+      const int page = slot_in_table < max_pages ? table[slot_in_table] : -1;
+      if (page < 0 || page >= num_pages) {
+        raise_fault(status, VOSTI_FAULT_PAGE_RANGE);
+        valid = false;
+      } else {
+        slot = ((int64_t)page * nkv + g) * page_size + (j % page_size);   // row of (page, head, offset)
+        const T* krow = k_cache + slot * dk;
+        float dot = 0.f;
+        for (int i = 0; i < dk; ++i) dot = fmaf(qs[i], to_f32(krow[i]), dot);
+        s = dot * scale_log2;
+        if (bias_h != nullptr) s += bias_h[min(pos - j, bias_last)];
+      }
+    }
+    const float tile_max = warp_max(s);
+    if (tile_max == -INFINITY) continue;  // nothing visible here: state untouched
+    const float m_new = fmaxf(m, tile_max);
+    const float alpha = exp2f(m - m_new);
+    const float p = valid ? exp2f(s - m_new) : 0.f;
+    l = l * alpha + warp_sum(p);
+#pragma unroll
+    for (int i = 0; i < MAX_W / 32; ++i) acc[i] *= alpha;
+    const int last = min(31, pos - j0);
+    for (int kk = 0; kk <= last; ++kk) {
+      const float pk = __shfl_sync(0xffffffffu, p, kk);
+      const int64_t sk = __shfl_sync(0xffffffffu, slot, kk);
+      if (pk == 0.f) continue;
+      const T* vrow = v_cache + sk * dv;
+#pragma unroll
+      for (int i = 0; i < MAX_W / 32; ++i) {
+        const int idx = lane + 32 * i;
+        if (idx < dv) acc[i] = fmaf(pk, to_f32(vrow[idx]), acc[i]);
+      }
+    }
+    m = m_new;
+  }
+  if (sink != nullptr) {
+    // the sink has a logit and nothing else: it joins the denominator once
+    const float s = sink[h] * LOG2E;
+    const float m_new = fmaxf(m, s);
+    const float alpha = exp2f(m - m_new);
+    l = l * alpha + exp2f(s - m_new);
+#pragma unroll
+    for (int i = 0; i < MAX_W / 32; ++i) acc[i] *= alpha;
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  T* orow = out + ((int64_t)t * nq + h) * dv;
+#pragma unroll
+  for (int i = 0; i < MAX_W / 32; ++i) {
+    const int idx = lane + 32 * i;
+    if (idx < dv) orow[idx] = from_f32<T>(acc[i] * inv);
+  }
+}
+}  // namespace
+
+// qkv: [tokens, nq*dk + nkv*dk + nkv*dv]; q_out: [tokens, nq*dk]; caches [pages, nkv, page_size, dk | dv].
+VOSTI_API int vosti_qkv_store(const void* qkv, void* q_out, void* k_cache, void* v_cache, const int* positions,
+                              const int* slot_mapping, int64_t num_slots, int page_size, int tokens, int nq, int nkv,
+                              int dk, int dv, float temp_coef, int temp_every, int is_f32, unsigned* status,
+                              cudaStream_t stream) {
+  VOSTI_REQUIRE(tokens >= 0 && nq > 0 && nkv >= 0 && dk > 0 && dv > 0, "qkv_store: bad sizes");
+  VOSTI_REQUIRE(temp_coef == 0.f || (temp_every > 0 && positions != nullptr), "qkv_store: the temperature needs positions and a positive period");
+  VOSTI_REQUIRE(k_cache == nullptr || (v_cache != nullptr && slot_mapping != nullptr && page_size > 0), "qkv_store: a cache needs slots");
+  if (tokens == 0) return VOSTI_OK;
+  if (is_f32)
+    vosti_launch(qkv_store_kernel<float>, dim3(tokens), dim3(256), 0, stream, (const float*)qkv, (float*)q_out, (float*)k_cache,
+                 (float*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, dk, dv, temp_coef, temp_every, status);
+  else
+    vosti_launch(qkv_store_kernel<bf16>, dim3(tokens), dim3(256), 0, stream, (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache,
+                 (bf16*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, dk, dv, temp_coef, temp_every, status);
+  VOSTI_LAUNCH_CHECK();
+}
+
+// q: [tokens, nq, dk]; out: [tokens, nq, dv]; bias: float32 [nq, bias_last + 1] in natural-log units
+// times log2(e), or null; sink: float32 [nq] in natural-log units, or null.
+VOSTI_API int vosti_attention_sink(const void* q, const void* k_cache, const void* v_cache, void* out, const int* positions,
+                                   const int* request_of, const int* block_table, int max_pages, int page_size,
+                                   int num_pages, int tokens, int nq, int nkv, int dk, int dv, float scale, int window,
+                                   const float* bias, int bias_last, const float* sink, int is_f32, unsigned* status,
+                                   cudaStream_t stream) {
+  VOSTI_REQUIRE(tokens >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention: bad head counts nq=%d nkv=%d", nq, nkv);
+  VOSTI_REQUIRE(dk > 0 && dv > 0 && dk <= MAX_W && dv <= MAX_W, "attention: head widths %d / %d must be at most %d", dk, dv, MAX_W);
+  VOSTI_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0, "attention: bad cache geometry");
+  VOSTI_REQUIRE(window >= 0 && (bias == nullptr || bias_last >= 0), "attention: bad window or bias table");
+  if (tokens == 0) return VOSTI_OK;
+  const int64_t warps = (int64_t)tokens * nq;
+  const int64_t blocks = (warps + WARPS - 1) / WARPS;
+  VOSTI_REQUIRE(blocks <= 0x7fffffffLL, "attention: too many (token, head) pairs");
+  const size_t smem = (size_t)WARPS * dk * sizeof(float);
+  if (is_f32)
+    vosti_launch(attention_sink_kernel<float>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, stream, (const float*)q,
+                 (const float*)k_cache, (const float*)v_cache, (float*)out, positions, request_of, block_table, max_pages,
+                 page_size, num_pages, tokens, nq, nkv, dk, dv, scale * LOG2E, window, bias, bias_last, sink, status);
+  else
+    vosti_launch(attention_sink_kernel<bf16>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, stream, (const bf16*)q,
+                 (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions, request_of, block_table, max_pages,
+                 page_size, num_pages, tokens, nq, nkv, dk, dv, scale * LOG2E, window, bias, bias_last, sink, status);
+  VOSTI_LAUNCH_CHECK();
+}

@@ -1,0 +1,310 @@
+// Gated delta rule: a recurrent mixer whose state per (request, head) is a float32 matrix
+// S [key channels, value channels], with one decay per (head, key channel).
+//
+// Per token and head, in this order:
+//   S <- diag(g) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+// so the read-out sees the token's own write. Around it: short causal convolutions with SiLU
+// on q, k and v (the last taps - 1 inputs of a request are part of its state), q and k made
+// unit vectors per head (q also times dk^-1/2), beta = sigmoid(.), g = exp(-exp(A_log) *
+// softplus(low-rank(h) + dt_bias)), and an output stage: o divided by its root mean square
+// over the value channels, times a weight, times sigmoid(low-rank gate).
+//
+// Everything after the projections is float32 in both serving types. A request's state slot
+// is one float32 vector: S for every head [heads, dk, dv], then the convolution tail
+// [taps - 1, conv channels].
+//
+// Kernels:
+//   delta_prep     one block per token: convolutions, unit vectors, beta, decay, gate
+//   delta_conv     one block per request: the convolution tail after this step
+//   delta_scan     one block per (request, head, 32 value columns): the recurrence over the
+//                  request's tokens of this step, from and to the state slot. Columns of S are
+//                  independent; a column's dk entries are spread over KS lanes of a warp.
+//   delta_out      one warp per (token, head): the output stage
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_TAPS = 16;
+constexpr int COLS = 32;        // value columns per block of the scan
+constexpr int ROWS = 32;        // key channels a lane keeps at most
+constexpr int TOKENS = 8;       // tokens staged in shared memory at a time
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+struct PrepArgs {
+  // the fused projection [tokens, stride]: columns q | k | v | beta | decay low-rank | gate low-rank
+  const void* proj;
+  int proj_f32, stride;
+  int off_q, off_k, off_v, off_beta, off_a, off_g;
+  int kv_heads, heads, dk, dv, taps, rank_a, rank_g;
+  const void* conv_w;           // [(2 kv_heads dk + heads dv), taps], the last column is the current token's
+  const void* a_log;            // [heads]
+  const void* dt_bias;          // [heads dk]
+  const void* a2;               // [heads dk, rank_a]
+  const void* g2;               // [heads dv, rank_g]
+  int w_f32;
+  const float* state;           // [slots, state_stride]
+  int64_t state_stride, conv_offset;
+  const int* request_of;
+  const int* cu_q;
+  const int* state_slots;
+  int num_slots;
+  float* q; float* k; float* v; float* beta; float* decay; float* gate;
+  unsigned* status;
+};
+
+__global__ void __launch_bounds__(256) delta_prep_kernel(PrepArgs a) {
+  extern __shared__ float smem[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int cq = a.kv_heads * a.dk, cv = a.heads * a.dv, cc = 2 * cq + cv;
+  float* y = smem;                        // [cc] convolved and activated q | k | v
+  float* low = smem + cc;                 // [rank_a + rank_g]
+  const int b = a.request_of[t];
+  const int local = t - a.cu_q[b];
+  int slot = a.state_slots[b];
+  if (slot < 0 || slot >= a.num_slots) {
+    if (threadIdx.x == 0) raise_fault(a.status, VOSTI_FAULT_SLOT_RANGE);
+    slot = 0;
+  }
+  const float* tail = a.state + (int64_t)slot * a.state_stride + a.conv_offset;   // [taps - 1, cc]
+  const int64_t row = (int64_t)t * a.stride;
+  // q | k | v occupy columns off_q .. off_q + cc of the projection in this order
+  for (int c = threadIdx.x; c < cc; c += blockDim.x) {
+    float acc = 0.f;
+    for (int i = 0; i < a.taps; ++i) {
+      const int back = a.taps - 1 - i;                  // how many tokens before this one
+      float x;
+      if (local - back >= 0) x = load_flex(a.proj, a.proj_f32, row - (int64_t)back * a.stride + a.off_q + c);
+      else x = tail[(int64_t)(a.taps - 1 + local - back) * cc + c];
+      acc = fmaf(load_flex(a.conv_w, a.w_f32, (int64_t)c * a.taps + i), x, acc);
+    }
+    y[c] = acc * sigmoidf_(acc);
+  }
+  for (int r = threadIdx.x; r < a.rank_a + a.rank_g; r += blockDim.x)
+    low[r] = load_flex(a.proj, a.proj_f32, row + (r < a.rank_a ? a.off_a + r : a.off_g + (r - a.rank_a)));
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  // unit vectors: one warp per q or k head
+  for (int head = warp; head < 2 * a.kv_heads; head += nwarps) {
+    const float* src = y + head * a.dk;
+    float ss = 0.f;
+    for (int i = lane; i < a.dk; i += 32) ss += src[i] * src[i];
+    ss = warp_sum(ss);
+    const bool is_q = head < a.kv_heads;
+    const float scale = (1.f / sqrtf(ss + 1e-6f)) * (is_q ? 1.f / sqrtf((float)a.dk) : 1.f);
+    float* dst = (is_q ? a.q : a.k) + (int64_t)t * cq + (is_q ? head : head - a.kv_heads) * a.dk;
+    for (int i = lane; i < a.dk; i += 32) dst[i] = src[i] * scale;
+  }
+  for (int c = threadIdx.x; c < cv; c += blockDim.x) a.v[(int64_t)t * cv + c] = y[2 * cq + c];
+  for (int h = threadIdx.x; h < a.heads; h += blockDim.x)
+    a.beta[(int64_t)t * a.heads + h] = sigmoidf_(load_flex(a.proj, a.proj_f32, row + a.off_beta + h));
+  const int cd = a.heads * a.dk;
+  for (int c = threadIdx.x; c < cd; c += blockDim.x) {
+    float rate = load_flex(a.dt_bias, a.w_f32, c);
+    for (int r = 0; r < a.rank_a; ++r) rate = fmaf(load_flex(a.a2, a.w_f32, (int64_t)c * a.rank_a + r), low[r], rate);
+    const float speed = expf(load_flex(a.a_log, a.w_f32, c / a.dk));
+    a.decay[(int64_t)t * cd + c] = expf(-speed * softplusf_(rate));
+  }
+  for (int c = threadIdx.x; c < cv; c += blockDim.x) {
+    float z = 0.f;
+    for (int r = 0; r < a.rank_g; ++r) z = fmaf(load_flex(a.g2, a.w_f32, (int64_t)c * a.rank_g + r), low[a.rank_a + r], z);
+    a.gate[(int64_t)t * cv + c] = sigmoidf_(z);
+  }
+}
+
+// The convolution tail of every request after this step: the last taps - 1 rows of
+// [old tail ; this step's projection rows]. A thread owns a channel, reads what it needs, then writes.
+__global__ void __launch_bounds__(256)
+delta_conv_kernel(const void* proj, int proj_f32, int stride, int off_q, int cc, int taps, float* state,
+                  int64_t state_stride, int64_t conv_offset, const int* cu_q, const int* state_slots, int num_slots) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = blockIdx.x;
+  const int slot = state_slots[b];
+  if (slot < 0 || slot >= num_slots) return;
+  const int start = cu_q[b], n = cu_q[b + 1] - start;
+  float* tail = state + (int64_t)slot * state_stride + conv_offset;
+  const int keep = taps - 1;
+  for (int c = threadIdx.x; c < cc; c += blockDim.x) {
+    float next[MAX_TAPS];
+    for (int r = 0; r < keep; ++r) {
+      const int idx = n + r;                 // row of [old tail (keep rows) ; projection rows (n)]
+      next[r] = idx < keep ? tail[(int64_t)idx * cc + c]
+                           : load_flex(proj, proj_f32, (int64_t)(start + idx - keep) * stride + off_q + c);
+    }
+    for (int r = 0; r < keep; ++r) tail[(int64_t)r * cc + c] = next[r];
+  }
+}
+
+// KS lanes share a column; lane part `ks` keeps rows ks, ks + KS, ... of it.
+template <int KS>
+__global__ void __launch_bounds__(COLS * KS)
+delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                  const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ out,
+                  float* state, int64_t state_stride, const int* __restrict__ cu_q, const int* __restrict__ state_slots,
+                  int num_slots, int kv_heads, int heads, int dk, int dv) {
+  extern __shared__ float smem[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
+  const int slot = state_slots[b];
+  if (slot < 0 || slot >= num_slots) return;
+  const int start = cu_q[b], n = cu_q[b + 1] - start;
+  const int g = h / (heads / kv_heads);
+  const int ks = threadIdx.x % KS, col = col0 + threadIdx.x / KS;
+  const bool live = col < dv;
+  float* S = state + (int64_t)slot * state_stride + (int64_t)h * dk * dv;
+  float s[ROWS];
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    const int r = ks + i * KS;
+    s[i] = (live && r < dk) ? S[(int64_t)r * dv + col] : 0.f;
+  }
+  float* sk = smem;                       // [TOKENS][dk]
+  float* sq = sk + TOKENS * dk;
+  float* sg = sq + TOKENS * dk;
+  float* sv = sg + TOKENS * dk;           // [TOKENS][COLS]
+  float* sb = sv + TOKENS * COLS;         // [TOKENS]
+  const int cq = kv_heads * dk, cd = heads * dk, cv = heads * dv;
+  for (int t0 = 0; t0 < n; t0 += TOKENS) {
+    const int count = min(TOKENS, n - t0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < count * dk; i += blockDim.x) {
+      const int64_t t = start + t0 + i / dk;
+      const int c = i % dk;
+      sk[i] = k[t * cq + g * dk + c];
+      sq[i] = q[t * cq + g * dk + c];
+      sg[i] = decay[t * cd + h * dk + c];
+    }
+    for (int i = threadIdx.x; i < count * COLS; i += blockDim.x) {
+      const int64_t t = start + t0 + i / COLS;
+      const int c = col0 + i % COLS;
+      sv[i] = c < dv ? v[t * cv + h * dv + c] : 0.f;
+    }
+    for (int i = threadIdx.x; i < count; i += blockDim.x) sb[i] = beta[(int64_t)(start + t0 + i) * heads + h];
+    __syncthreads();
+    for (int tt = 0; tt < count; ++tt) {
+      const float* kt = sk + tt * dk;
+      const float* qt = sq + tt * dk;
+      const float* gt = sg + tt * dk;
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < ROWS; ++i) {
+        const int r = ks + i * KS;
+        if (r < dk) {
+          s[i] *= gt[r];
+          dot = fmaf(s[i], kt[r], dot);
+        }
+      }
+#pragma unroll
+      for (int o = KS / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float u = sb[tt] * (sv[tt * COLS + threadIdx.x / KS] - dot);
+      float read = 0.f;
+#pragma unroll
+      for (int i = 0; i < ROWS; ++i) {
+        const int r = ks + i * KS;
+        if (r < dk) {
+          s[i] = fmaf(kt[r], u, s[i]);
+          read = fmaf(s[i], qt[r], read);
+        }
+      }
+#pragma unroll
+      for (int o = KS / 2; o > 0; o >>= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
+      if (ks == 0 && live) out[(int64_t)(start + t0 + tt) * cv + h * dv + col] = read;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    const int r = ks + i * KS;
+    if (live && r < dk) S[(int64_t)r * dv + col] = s[i];
+  }
+}
+
+// y[t, h, :] = o / sqrt(mean(o^2) + eps) * w * gate, in the serving type, for the output projection.
+template <typename TO>
+__global__ void __launch_bounds__(128)
+delta_out_kernel(const float* __restrict__ o, const float* __restrict__ gate, const void* __restrict__ w, int w_f32,
+                 TO* __restrict__ y, int64_t pairs, int dv, float eps) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int64_t pair = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (pair >= pairs) return;
+  const float* src = o + pair * dv;
+  float ss = 0.f;
+  for (int i = lane; i < dv; i += 32) ss += src[i] * src[i];
+  ss = warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / (float)dv + eps);
+  for (int i = lane; i < dv; i += 32)
+    y[pair * dv + i] = from_f32<TO>(src[i] * inv * load_flex(w, w_f32, i) * gate[pair * dv + i]);
+}
+
+}  // namespace
+
+VOSTI_API int vosti_delta_prep(const void* proj, int proj_f32, int stride, int off_q, int off_k, int off_v, int off_beta,
+                               int off_a, int off_g, int kv_heads, int heads, int dk, int dv, int taps, int rank_a,
+                               int rank_g, const void* conv_w, const void* a_log, const void* dt_bias, const void* a2,
+                               const void* g2, int w_f32, float* state, int64_t state_stride, int64_t conv_offset,
+                               const int* request_of, const int* cu_q, const int* state_slots, int num_slots,
+                               int requests, int tokens, float* q, float* k, float* v, float* beta, float* decay,
+                               float* gate, unsigned* status, cudaStream_t stream) {
+  VOSTI_REQUIRE(kv_heads > 0 && heads > 0 && heads % kv_heads == 0 && dk > 0 && dv > 0, "delta_prep: bad head sizes");
+  VOSTI_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "delta_prep: %d taps (1 to %d are taken)", taps, MAX_TAPS);
+  VOSTI_REQUIRE(off_k == off_q + kv_heads * dk && off_v == off_k + kv_heads * dk, "delta_prep: q, k, v must be adjacent columns");
+  if (tokens == 0) return VOSTI_OK;
+  PrepArgs a = {};
+  a.proj = proj; a.proj_f32 = proj_f32; a.stride = stride;
+  a.off_q = off_q; a.off_k = off_k; a.off_v = off_v; a.off_beta = off_beta; a.off_a = off_a; a.off_g = off_g;
+  a.kv_heads = kv_heads; a.heads = heads; a.dk = dk; a.dv = dv; a.taps = taps; a.rank_a = rank_a; a.rank_g = rank_g;
+  a.conv_w = conv_w; a.a_log = a_log; a.dt_bias = dt_bias; a.a2 = a2; a.g2 = g2; a.w_f32 = w_f32;
+  a.state = state; a.state_stride = state_stride; a.conv_offset = conv_offset;
+  a.request_of = request_of; a.cu_q = cu_q; a.state_slots = state_slots; a.num_slots = num_slots;
+  a.q = q; a.k = k; a.v = v; a.beta = beta; a.decay = decay; a.gate = gate; a.status = status;
+  const int cc = 2 * kv_heads * dk + heads * dv;
+  const size_t smem = (size_t)(cc + rank_a + rank_g) * sizeof(float);
+  VOSTI_REQUIRE(smem <= 200 * 1024, "delta_prep: %d channels do not fit shared memory", cc);
+  if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  vosti_launch(delta_prep_kernel, dim3(tokens), dim3(256), smem, stream, a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { vosti_set_error("%s", cudaGetErrorString(e)); return (int)e; }
+  // the tail is rewritten only after every token of the step has read the old one
+  if (taps > 1)
+    vosti_launch(delta_conv_kernel, dim3(requests), dim3(256), 0, stream, proj, proj_f32, stride, off_q, cc, taps, state,
+                 state_stride, conv_offset, cu_q, state_slots, num_slots);
+  VOSTI_LAUNCH_CHECK();
+}
+
+VOSTI_API int vosti_delta_scan(const float* q, const float* k, const float* v, const float* beta, const float* decay,
+                               float* out, float* state, int64_t state_stride, const int* cu_q, const int* state_slots,
+                               int num_slots, int requests, int kv_heads, int heads, int dk, int dv, cudaStream_t stream) {
+  VOSTI_REQUIRE(kv_heads > 0 && heads > 0 && heads % kv_heads == 0 && dk > 0 && dv > 0, "delta_scan: bad head sizes");
+  VOSTI_REQUIRE(dk <= ROWS * 8, "delta_scan: %d key channels (at most %d are taken)", dk, ROWS * 8);
+  VOSTI_REQUIRE(heads <= 65535 && (dv + COLS - 1) / COLS <= 65535, "delta_scan: too many heads or value channels");
+  if (requests == 0) return VOSTI_OK;
+  const dim3 grid(requests, heads, (dv + COLS - 1) / COLS);
+  const size_t smem = (size_t)(TOKENS * (3 * dk + COLS) + TOKENS) * sizeof(float);
+  const int ks = dk <= ROWS ? 1 : dk <= 2 * ROWS ? 2 : dk <= 4 * ROWS ? 4 : 8;
+#define VOSTI_SCAN(KS)                                                                                              \
+  vosti_launch(delta_scan_kernel<KS>, grid, dim3(COLS * KS), smem, stream, q, k, v, beta, decay, out, state,       \
+               state_stride, cu_q, state_slots, num_slots, kv_heads, heads, dk, dv)
+  if (ks == 1) VOSTI_SCAN(1);
+  else if (ks == 2) VOSTI_SCAN(2);
+  else if (ks == 4) VOSTI_SCAN(4);
+  else VOSTI_SCAN(8);
+#undef VOSTI_SCAN
+  VOSTI_LAUNCH_CHECK();
+}
+
+VOSTI_API int vosti_delta_out(const float* o, const float* gate, const void* w, int w_f32, void* y, int y_f32, int tokens,
+                              int heads, int dv, float eps, cudaStream_t stream) {
+  VOSTI_REQUIRE(tokens >= 0 && heads > 0 && dv > 0, "delta_out: bad sizes");
+  if (tokens == 0) return VOSTI_OK;
+  const int64_t pairs = (int64_t)tokens * heads;
+  const unsigned blocks = (unsigned)((pairs + 3) / 4);
+  if (y_f32) vosti_launch(delta_out_kernel<float>, dim3(blocks), dim3(128), 0, stream, o, gate, w, w_f32, (float*)y, pairs, dv, eps);
+  else vosti_launch(delta_out_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, o, gate, w, w_f32, (bf16*)y, pairs, dv, eps);
+  VOSTI_LAUNCH_CHECK();
+}

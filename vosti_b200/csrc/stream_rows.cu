@@ -1,0 +1,139 @@
+// Row kernels for models that keep their residual stream in float32 whatever the serving
+// type: the deferred residual sum, Dynamic Tanh (a norm without statistics), the packing of
+// [stream ; first embedding] for a loop's re-entry product, and the merge of side-by-side
+// mixer branches (each divided by its root mean square, weighted, averaged).
+//
+// The stream is float32 [rows, width]. A sublayer's output ("term") is float32 or the serving
+// type; up to two terms wait to be added (mixer and feed-forward of a parallel block), and the
+// kernel that next reads the stream adds them in a fixed order: (stream + term 1) + term 2.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float term_at(const void* p, int is_f32, int64_t i) {
+  return p == nullptr ? 0.f : load_flex(p, is_f32, i);
+}
+
+// x = stream + t1 + t2 (any of them absent); stream_out <- x; out <- tanh(alpha x) * w + b.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+dyt_kernel(const float* stream, const void* t1, int t1_f32, const void* t2, int t2_f32, float* stream_out,
+           const void* __restrict__ weight, const void* __restrict__ bias, int wb_f32, float alpha,
+           TO* __restrict__ out, int width) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t base = (int64_t)blockIdx.x * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float x = stream != nullptr ? stream[base + i] : 0.f;
+    if (t1 != nullptr) x += load_flex(t1, t1_f32, base + i);
+    if (t2 != nullptr) x += load_flex(t2, t2_f32, base + i);
+    if (stream_out != nullptr) stream_out[base + i] = x;
+    float y = tanhf(alpha * x) * load_flex(weight, wb_f32, i);
+    if (bias != nullptr) y += load_flex(bias, wb_f32, i);
+    out[base + i] = from_f32<TO>(y);
+  }
+}
+
+// out[r, 0:width] = stream + t1 + t2; out[r, width:width+tail_width] = tail[r] (optional).
+template <typename TO>
+__global__ void __launch_bounds__(256)
+stream_sum_kernel(const float* stream, const void* t1, int t1_f32, const void* t2, int t2_f32, TO* out,
+                  int64_t out_stride, const void* __restrict__ tail, int tail_f32, int tail_width, int width) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t base = (int64_t)blockIdx.x * width;
+  TO* dst = out + (int64_t)blockIdx.x * out_stride;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float x = stream != nullptr ? stream[base + i] : 0.f;
+    x += term_at(t1, t1_f32, base + i);
+    x += term_at(t2, t2_f32, base + i);
+    dst[i] = from_f32<TO>(x);
+  }
+  if (tail != nullptr) {
+    const int64_t tbase = (int64_t)blockIdx.x * tail_width;
+    for (int i = threadIdx.x; i < tail_width; i += blockDim.x) dst[width + i] = from_f32<TO>(load_flex(tail, tail_f32, tbase + i));
+  }
+}
+
+constexpr int MAX_BRANCHES = 4;
+struct Branches {
+  const void* x[MAX_BRANCHES];       // [rows, width], float32 or bfloat16
+  const void* w[MAX_BRANCHES];       // [width]
+  int x_f32[MAX_BRANCHES];
+  int count;
+};
+
+// out = (1 / count) * sum_b  x_b / sqrt(mean(x_b^2) + eps) * w_b, float32.
+__global__ void __launch_bounds__(256)
+branch_merge_kernel(Branches br, int w_f32, float* __restrict__ out, int width, float eps) {
+  __shared__ float scratch[32];
+  __shared__ float inv_rms[MAX_BRANCHES];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t base = (int64_t)blockIdx.x * width;
+  for (int b = 0; b < br.count; ++b) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      const float v = load_flex(br.x[b], br.x_f32[b], base + i);
+      ss += v * v;
+    }
+    const float total = block_sum(ss, scratch);
+    if (threadIdx.x == 0) inv_rms[b] = 1.f / sqrtf(total / (float)width + eps);
+  }
+  __syncthreads();
+  const float share = 1.f / (float)br.count;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float acc = 0.f;
+    for (int b = 0; b < br.count; ++b)
+      acc += load_flex(br.x[b], br.x_f32[b], base + i) * inv_rms[b] * load_flex(br.w[b], w_f32, i);
+    out[base + i] = acc * share;
+  }
+}
+
+}  // namespace
+
+VOSTI_API int vosti_dyt(const float* stream, const void* t1, int t1_f32, const void* t2, int t2_f32, float* stream_out,
+                        const void* weight, const void* bias, int wb_f32, float alpha, void* out, int out_f32, int rows,
+                        int width, cudaStream_t stream_id) {
+  VOSTI_REQUIRE(rows >= 0 && width > 0, "dyt: bad sizes rows=%d width=%d", rows, width);
+  VOSTI_REQUIRE(stream != nullptr || t1 != nullptr, "dyt: nothing to norm");
+  if (rows == 0) return VOSTI_OK;
+  if (out_f32)
+    vosti_launch(dyt_kernel<float>, dim3(rows), dim3(256), 0, stream_id, stream, t1, t1_f32, t2, t2_f32, stream_out, weight,
+                 bias, wb_f32, alpha, (float*)out, width);
+  else
+    vosti_launch(dyt_kernel<bf16>, dim3(rows), dim3(256), 0, stream_id, stream, t1, t1_f32, t2, t2_f32, stream_out, weight,
+                 bias, wb_f32, alpha, (bf16*)out, width);
+  VOSTI_LAUNCH_CHECK();
+}
+
+VOSTI_API int vosti_stream_sum(const float* stream, const void* t1, int t1_f32, const void* t2, int t2_f32, void* out,
+                               int out_f32, int64_t out_stride, const void* tail, int tail_f32, int tail_width, int rows,
+                               int width, cudaStream_t stream_id) {
+  VOSTI_REQUIRE(rows >= 0 && width > 0 && out_stride >= width + (tail ? tail_width : 0),
+                "stream_sum: bad sizes rows=%d width=%d", rows, width);
+  if (rows == 0) return VOSTI_OK;
+  if (out_f32)
+    vosti_launch(stream_sum_kernel<float>, dim3(rows), dim3(256), 0, stream_id, stream, t1, t1_f32, t2, t2_f32, (float*)out,
+                 out_stride, tail, tail_f32, tail_width, width);
+  else
+    vosti_launch(stream_sum_kernel<bf16>, dim3(rows), dim3(256), 0, stream_id, stream, t1, t1_f32, t2, t2_f32, (bf16*)out,
+                 out_stride, tail, tail_f32, tail_width, width);
+  VOSTI_LAUNCH_CHECK();
+}
+
+VOSTI_API int vosti_branch_merge(const void* const* xs, const int* x_f32, const void* const* ws, int w_f32, int count,
+                                 float* out, int rows, int width, float eps, cudaStream_t stream_id) {
+  VOSTI_REQUIRE(count >= 1 && count <= MAX_BRANCHES, "branch_merge: %d branches (1 to %d are taken)", count, MAX_BRANCHES);
+  VOSTI_REQUIRE(rows >= 0 && width > 0, "branch_merge: bad sizes rows=%d width=%d", rows, width);
+  if (rows == 0) return VOSTI_OK;
+  Branches br = {};
+  br.count = count;
+  for (int b = 0; b < count; ++b) {
+    br.x[b] = xs[b];
+    br.w[b] = ws[b];
+    br.x_f32[b] = x_f32[b];
+  }
+  vosti_launch(branch_merge_kernel, dim3(rows), dim3(256), 0, stream_id, br, w_f32, out, width, eps);
+  VOSTI_LAUNCH_CHECK();
+}

@@ -76,8 +76,7 @@ class ModelRunner:
         if consume_tensors:
             tensors.clear()
             torch.cuda.empty_cache()
-        cache_specs = [b.mixer.cache_spec() for b in self.model.blocks]
-        state_specs = [b.mixer.state_spec() for b in self.model.blocks]
+        cache_specs, state_specs = self.model.cache_specs()      # one per (layer, run) that owns a cache
         self.cache = CacheManager(cache_specs, state_specs, num_pages=num_pages, page_size=page_size,
                                   max_requests=max_requests, device=self.device, dtype=self.dtype,
                                   prefix_reuse=prefix_reuse)

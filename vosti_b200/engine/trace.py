@@ -17,7 +17,7 @@ import numpy as np
 from .batch import StepEntry
 from .runner import ModelRunner
 
-MAX_LIVE = 8
+MAX_LIVE = 4      # requests live at any time: state slots are used again by later requests
 
 
 class TraceReplayer:

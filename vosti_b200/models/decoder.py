@@ -14,7 +14,7 @@ import torch
 
 from .. import ops
 from ..config.schema import ModelSpec
-from ..parts import build_block, build_embedding, build_head, build_norm
+from ..parts import Part, build_block, build_embedding, build_head, build_norm, build_reentry
 from ..weights.loader import WeightSpec
 
 
@@ -26,6 +26,15 @@ class DecoderModel:
         self.final_norm = build_norm(spec.final_norm, spec.hidden_size)
         self.embedding = build_embedding(spec.embedding, spec.hidden_size, spec.vocab_size)
         self.head = build_head(spec.head, spec.hidden_size, spec.vocab_size, spec.tie_word_embeddings)
+        self.reentry = build_reentry(spec.reentry, spec.hidden_size)
+        # One cache (pages and state slot storage) per (layer, instance) that owns one. Cache i
+        # belongs to layer i's first run; further runs of a layer get caches after those.
+        self.cache_index = {(i, 0): i for i in range(len(self.blocks))}
+        self.cache_layers = list(range(len(self.blocks)))
+        for entry in spec.run_order:
+            if entry.cache_from is None and (entry.layer, entry.instance) not in self.cache_index:
+                self.cache_index[(entry.layer, entry.instance)] = len(self.cache_layers)
+                self.cache_layers.append(entry.layer)
         self.device = None
         self.dtype = None
 
@@ -40,6 +49,13 @@ class DecoderModel:
                 yield position
         yield self.final_norm
         yield self.head
+        if self.reentry is not None:
+            yield self.reentry
+
+    def cache_specs(self):
+        """(paged cache spec, state spec) of every cache in `cache_layers` order."""
+        return ([self.blocks[i].mixer.cache_spec() for i in self.cache_layers],
+                [self.blocks[i].mixer.state_spec() for i in self.cache_layers])
 
     @property
     def capture_safe(self) -> bool:
@@ -56,20 +72,31 @@ class DecoderModel:
         `weight` tensor; its other tensors (a bias) stand beside it."""
         return name[: -len("weight")] if name.endswith("weight") else name + "."
 
-    def _final_norm_prefix(self) -> str:
-        return self._prefix_of(self.spec.final_norm_name)
+    @classmethod
+    def _tensor_name(cls, name: str, key: str) -> str:
+        """Checkpoint name of a model-level part's tensor `key`, given the name of its `weight`."""
+        return name if key == "weight" else cls._prefix_of(name) + key
+
+    @classmethod
+    def _own(cls, tensors, name: str, part):
+        """The tensors of a model-level part, by the part's own keys."""
+        return {key: tensors[cls._tensor_name(name, key)] for key in part.weight_specs()
+                if cls._tensor_name(name, key) in tensors}
 
     def expected_weights(self) -> Dict[str, WeightSpec]:
         spec = self.spec
-        out = {self._prefix_of(spec.embed_name) + key: w for key, w in self.embedding.weight_specs().items()}
+        out = {self._tensor_name(spec.embed_name, key): w for key, w in self.embedding.weight_specs().items()}
         for i, block in enumerate(self.blocks):
             prefix = spec.layer_prefix.format(i=i)
             for key, w in block.weight_specs().items():
                 out[prefix + key] = w
         for key, w in self.final_norm.weight_specs().items():
-            out[self._final_norm_prefix() + key] = w
+            out[self._tensor_name(spec.final_norm_name, key)] = w
         for key, w in self.head.weight_specs().items():
-            out[self._prefix_of(spec.lm_head_name) + key] = w
+            out[self._tensor_name(spec.lm_head_name, key)] = w
+        if self.reentry is not None:
+            for key, w in self.reentry.weight_specs().items():
+                out[self._tensor_name(spec.reentry_name, key)] = w
         return out
 
     def ignorable_weights(self):
@@ -85,16 +112,17 @@ class DecoderModel:
     def load(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype) -> None:
         spec = self.spec
         under = lambda prefix: {k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}
-        self.embedding.load(under(self._prefix_of(spec.embed_name)), dtype)
+        self.embedding.load(self._own(tensors, spec.embed_name, self.embedding), dtype)
         for i, block in enumerate(self.blocks):
             block.load(under(spec.layer_prefix.format(i=i)), dtype)
-        self.final_norm.load(under(self._final_norm_prefix()), dtype)
-        expected = self.head.weight_specs()
-        head_tensors = {k: v for k, v in under(self._prefix_of(spec.lm_head_name)).items() if k in expected}
-        self.head.load(head_tensors, dtype, tied=self.embedding.table() if spec.tie_word_embeddings else None)
+        self.final_norm.load(self._own(tensors, spec.final_norm_name, self.final_norm), dtype)
+        self.head.load(self._own(tensors, spec.lm_head_name, self.head), dtype,
+                       tied=self.embedding.table() if spec.tie_word_embeddings else None)
+        if self.reentry is not None:
+            self.reentry.load(self._own(tensors, spec.reentry_name, self.reentry), dtype)
         self.device = next(iter(tensors.values())).device
         self.dtype = dtype
-        for part in (self.embedding, self.final_norm, self.head):
+        for part in (self.embedding, self.final_norm, self.head) + ((self.reentry,) if self.reentry is not None else ()):
             part.setup(self.device, dtype)
         for block in self.blocks:
             block.setup(self.device, dtype)
@@ -115,10 +143,23 @@ class DecoderModel:
                     if base not in seen:
                         seen.add(base)
                         total += value.untyped_storage().nbytes()
+                elif isinstance(value, (list, tuple)):
+                    # parts inside a part (the branches of a mixer) and lists of tensors
+                    for item in value:
+                        for inner in (item if isinstance(item, tuple) else (item,)):
+                            if isinstance(inner, Part):
+                                visit(inner)
+                            elif isinstance(inner, torch.Tensor) and inner.is_cuda:
+                                base = inner.untyped_storage().data_ptr()
+                                if base not in seen:
+                                    seen.add(base)
+                                    total += inner.untyped_storage().nbytes()
         for block in self.blocks:
             for _, part in block._children():
                 visit(part)
         visit(self.final_norm)
+        if self.reentry is not None:
+            visit(self.reentry)
         visit(self.head)          # a tied head is the embedding table, read whole by the head's product
         return total
 
@@ -129,16 +170,23 @@ class DecoderModel:
         source = ctx.extras.get("feedback") if ctx.extras else None
         hidden = self.embedding.forward(ctx, ctx.tokens,
                                         feedback=None if source is None else (source, ctx.feedback_values))
+        first = hidden                      # the embedding output, which a re-entry reads again
         residual: Optional[torch.Tensor] = None
         for entry in self.spec.run_order:
             owner = entry.layer if entry.cache_from is None else entry.cache_from
+            if entry.reenter:
+                hidden, residual = self.reentry.forward(ctx, hidden, residual, first)
             hidden, residual = self.blocks[entry.layer].forward(
-                ctx, hidden, residual, layer_caches[owner], writes_cache=entry.cache_from is None)
+                ctx, hidden, residual, layer_caches[self.cache_index[(owner, entry.instance)]],
+                writes_cache=entry.cache_from is None)
         return hidden, residual
 
     def logits(self, ctx, hidden: torch.Tensor, residual: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         """float32 logits [len(rows), vocab] of the rows (flat token indices) asked for:
         only those rows are gathered, added, normed and multiplied with the head."""
+        if isinstance(hidden, ops.DeferredSum):
+            # a float32 stream with sublayer outputs still to be added: add, then gather
+            hidden, residual = ops.stream_sum(residual, hidden), None
         hidden = ops.gather_rows(ops.materialize(hidden), rows, ctx.status)
         if residual is None:
             final = self.final_norm.forward(ctx, hidden)

@@ -635,3 +635,199 @@ def attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
                           count=lists["num_long_rows"], cu_q=ctx.cu_q, kv_len=ctx.kv_len,
                           max_q_len=lists["max_long_q_len"], **common)
     return out
+
+
+# ---------------------------------------------------------------- float32 residual stream
+class DeferredSum:
+    """Sublayer outputs [rows, width] that still have to be added to the residual stream: the
+    kernel that next reads the stream (a norm with `forward_add`, `stream_sum`) adds them in
+    order, in float32. `materialize` gives their sum alone."""
+
+    def __init__(self, *terms):
+        self.terms = tuple(materialize(t) for t in terms if t is not None)
+        if not 1 <= len(self.terms) <= 2:
+            raise KernelError("a deferred sum holds one or two terms")
+        self.shape = tuple(self.terms[0].shape)
+
+    def materialize(self) -> torch.Tensor:
+        return stream_sum(None, self)
+
+
+def _terms(x):
+    """Up to two addends as (pointer, is_f32) pairs."""
+    if x is None:
+        terms = ()
+    elif isinstance(x, DeferredSum):
+        terms = x.terms
+    else:
+        terms = (materialize(x),)
+    _contig(*terms)
+    flat = []
+    for t in terms:
+        flat += [_p(t), _is_f32(t)]
+    while len(flat) < 4:
+        flat += [None, 0]
+    return terms, flat
+
+
+def dyt(x, weight: torch.Tensor, bias: Optional[torch.Tensor], alpha: float, out_dtype: torch.dtype,
+        stream: Optional[torch.Tensor] = None, stream_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Dynamic Tanh of s = stream + x (x: a tensor, a `DeferredSum` or None; stream: float32 or None):
+    tanh(alpha * s) * weight + bias in float32, rounded to `out_dtype`; s itself goes to
+    `stream_out` (float32, may be `stream`)."""
+    terms, flat = _terms(x)
+    like = stream if stream is not None else terms[0]
+    _contig(stream, stream_out, weight, bias)
+    if stream is not None and stream.dtype != torch.float32 or stream_out is not None and stream_out.dtype != torch.float32:
+        raise KernelError("dyt: the residual stream is float32")
+    if bias is not None and bias.dtype != weight.dtype:
+        raise KernelError("dyt: weight and bias must share a dtype")
+    rows, width = like.shape
+    out = torch.empty((rows, width), dtype=out_dtype, device=like.device)
+    _check(library().vosti_dyt(_p(stream), *flat, _p(stream_out), _p(weight), _p(bias), _is_f32(weight),
+                               ctypes.c_float(alpha), _p(out), _is_f32(out), rows, width, _stream()), "dyt")
+    return out
+
+
+def stream_sum(stream: Optional[torch.Tensor], x, *, out_dtype: torch.dtype = torch.float32,
+               tail: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """stream + x in float32, rounded to `out_dtype`; with `tail` [rows, w] the result is
+    [rows, width + w] with the tail's rows appended to the sum's (the operand of a product with
+    a [.., width + w] weight)."""
+    terms, flat = _terms(x)
+    like = stream if stream is not None else terms[0]
+    _contig(stream, tail)
+    rows, width = like.shape
+    tail_width = 0 if tail is None else tail.shape[1]
+    out = torch.empty((rows, width + tail_width), dtype=out_dtype, device=like.device)
+    _check(library().vosti_stream_sum(_p(stream), *flat, _p(out), _is_f32(out), ctypes.c_int64(width + tail_width),
+                                      _p(tail), 0 if tail is None else _is_f32(tail), tail_width, rows, width,
+                                      _stream()), "stream_sum")
+    return out
+
+
+def branch_merge(xs, weights, eps: float) -> torch.Tensor:
+    """mean over branches of x_b / sqrt(mean(x_b^2) + eps) * w_b, float32 [rows, width]."""
+    xs = [materialize(x) for x in xs]
+    _contig(*xs, *weights)
+    count = len(xs)
+    rows, width = xs[0].shape
+    flag = _is_f32(weights[0])
+    if any(_is_f32(w) != flag for w in weights) or any(tuple(x.shape) != (rows, width) for x in xs):
+        raise KernelError("branch_merge: branches must share a shape and their weights a dtype")
+    out = torch.empty((rows, width), dtype=torch.float32, device=xs[0].device)
+    x_ptrs = (ctypes.c_void_p * count)(*[x.data_ptr() for x in xs])
+    w_ptrs = (ctypes.c_void_p * count)(*[w.data_ptr() for w in weights])
+    kinds = (ctypes.c_int * count)(*[_is_f32(x) for x in xs])
+    _check(library().vosti_branch_merge(x_ptrs, kinds, w_ptrs, flag, count, _p(out), rows, width, ctypes.c_float(eps),
+                                        _stream()), "branch_merge")
+    return out
+
+
+# ---------------------------------------------------------------- attention with bias and sink
+def qkv_store(qkv: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], *, nq: int, nkv: int,
+              dk: int, dv: int, page_size: int, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+              temp_coef: float, temp_every: int, status: torch.Tensor) -> torch.Tensor:
+    """After a q | k | v projection without rotation: the queries times their temperature
+    (1 + coef * ln(floor((p + 1) / every) + 1), 1 if coef is 0) are returned [tokens, nq * dk];
+    keys and values go to their cache slots (caches of different widths)."""
+    qkv = materialize(qkv)
+    _contig(qkv, k_cache, v_cache, positions, slot_mapping)
+    flag = _same_dtype(qkv, k_cache, v_cache)
+    tokens = qkv.shape[0]
+    if qkv.shape[1] != nq * dk + nkv * (dk + dv):
+        raise KernelError("qkv_store: input width does not match the head counts")
+    q = torch.empty((tokens, nq * dk), dtype=qkv.dtype, device=qkv.device)
+    num_slots = 0 if k_cache is None else k_cache.numel() // (nkv * dk)
+    _check(library().vosti_qkv_store(_p(qkv), _p(q), _p(k_cache), _p(v_cache), _p(positions), _p(slot_mapping),
+                                     ctypes.c_int64(num_slots), page_size, tokens, nq, nkv, dk, dv,
+                                     ctypes.c_float(temp_coef), int(temp_every), flag, _p(status), _stream()), "qkv_store")
+    return q
+
+
+def attention_sink(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, *, nq: int, nkv: int,
+                   dk: int, dv: int, scale: float, window: int, bias: Optional[torch.Tensor],
+                   sink: Optional[torch.Tensor]) -> torch.Tensor:
+    """Causal attention of every query row over its request's cached keys, with an optional bias
+    table float32 [nq, distances] (base-2 units, the last column serving every larger distance)
+    and an optional sink logit per head (float32 [nq], natural units). Returns [tokens, nq * dv]."""
+    _contig(q, k_cache, v_cache, bias, sink)
+    flag = _same_dtype(q, k_cache, v_cache)
+    tokens = q.shape[0]
+    out = torch.empty((tokens, nq * dv), dtype=q.dtype, device=q.device)
+    num_pages = k_cache.numel() // (group.page_size * nkv * dk)
+    _check(library().vosti_attention_sink(
+        _p(q), _p(k_cache), _p(v_cache), _p(out), _p(ctx.positions), _p(ctx.request_of), _p(group.block_table),
+        group.block_table.shape[1], group.page_size, num_pages, tokens, nq, nkv, dk, dv, ctypes.c_float(scale), window,
+        _p(bias), 0 if bias is None else bias.shape[1] - 1, _p(sink), flag, _p(ctx.status), _stream()), "attention_sink")
+    return out
+
+
+# ---------------------------------------------------------------- gated delta rule
+def delta_prep(proj: torch.Tensor, offsets: dict, *, kv_heads: int, heads: int, dk: int, dv: int, taps: int, rank_a: int,
+               rank_g: int, conv_w, a_log, dt_bias, a2, g2, state: torch.Tensor, conv_offset: int, ctx):
+    """Everything between the fused projection and the recurrence (see csrc/delta_rule.cu); also
+    moves the convolution tail in the requests' state slots on. Returns float32 q, k, v, beta,
+    decay, gate."""
+    proj = materialize(proj)
+    small = (conv_w, a_log, dt_bias, a2, g2)
+    _contig(proj, state, *small)
+    flag = _is_f32(conv_w)
+    if any(_is_f32(t) != flag for t in small) or state.dtype != torch.float32:
+        raise KernelError("delta_prep: the small tensors must share a dtype and the state is float32")
+    tokens, dev = proj.shape[0], proj.device
+    new = lambda width: torch.empty((tokens, width), dtype=torch.float32, device=dev)
+    q, k, v = new(kv_heads * dk), new(kv_heads * dk), new(heads * dv)
+    beta, decay, gate = new(heads), new(heads * dk), new(heads * dv)
+    _check(library().vosti_delta_prep(
+        _p(proj), _is_f32(proj), proj.shape[1], offsets["q"], offsets["k"], offsets["v"], offsets["b"], offsets["a"],
+        offsets["g"], kv_heads, heads, dk, dv, taps, rank_a, rank_g, _p(conv_w), _p(a_log), _p(dt_bias), _p(a2), _p(g2),
+        flag, _p(state), ctypes.c_int64(state.shape[1]), ctypes.c_int64(conv_offset), _p(ctx.request_of), _p(ctx.cu_q),
+        _p(ctx.state_slots), state.shape[0], ctx.num_requests, tokens, _p(q), _p(k), _p(v), _p(beta), _p(decay), _p(gate),
+        _p(ctx.status), _stream()), "delta_prep", kernels=2 if taps > 1 else 1)
+    return q, k, v, beta, decay, gate
+
+
+def delta_scan(q, k, v, beta, decay, state: torch.Tensor, ctx, *, kv_heads: int, heads: int, dk: int, dv: int) -> torch.Tensor:
+    """The recurrence over every request's tokens of this step, from and to its state slot;
+    returns the read-outs, float32 [tokens, heads * dv]."""
+    _contig(q, k, v, beta, decay, state)
+    out = torch.empty((q.shape[0], heads * dv), dtype=torch.float32, device=q.device)
+    _check(library().vosti_delta_scan(_p(q), _p(k), _p(v), _p(beta), _p(decay), _p(out), _p(state),
+                                      ctypes.c_int64(state.shape[1]), _p(ctx.cu_q), _p(ctx.state_slots), state.shape[0],
+                                      ctx.num_requests, kv_heads, heads, dk, dv, _stream()), "delta_scan")
+    return out
+
+
+def delta_out(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, *, heads: int, dv: int,
+              out_dtype: torch.dtype) -> torch.Tensor:
+    """o / sqrt(mean(o^2) + eps) * weight * gate per (token, head), rounded to `out_dtype`."""
+    _contig(o, gate, weight)
+    y = torch.empty(o.shape, dtype=out_dtype, device=o.device)
+    _check(library().vosti_delta_out(_p(o), _p(gate), _p(weight), _is_f32(weight), _p(y), _is_f32(y), o.shape[0], heads, dv,
+                                     ctypes.c_float(eps), _stream()), "delta_out")
+    return y
+
+
+# ---------------------------------------------------------------- mixture of experts
+def moe_route(logits: torch.Tensor, top: int):
+    """The `top` largest of each row of float32 router logits: (expert ids int32 [tokens, top],
+    their softmax weights float32 [tokens, top], the same weights as a dense [tokens, experts])."""
+    if logits.dtype != torch.float32:
+        raise KernelError("moe_route: router logits are float32")
+    _contig(logits)
+    tokens, experts = logits.shape
+    chosen = torch.empty((tokens, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=logits.device)
+    dense = torch.empty((tokens, experts), dtype=torch.float32, device=logits.device)
+    _check(library().vosti_moe_route(_p(logits), tokens, experts, top, _p(chosen), _p(weights), _p(dense), _stream()),
+           "moe_route")
+    return chosen, weights, dense
+
+
+def moe_scale(act: torch.Tensor, dense: torch.Tensor, ff: int) -> torch.Tensor:
+    """act[t, e * ff + i] *= dense[t, e], in place."""
+    _contig(act, dense)
+    _check(library().vosti_moe_scale(_p(act), _p(dense), act.shape[0], dense.shape[1], ff, _is_f32(act), _stream()),
+           "moe_scale")
+    return act

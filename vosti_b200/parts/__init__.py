@@ -1,12 +1,16 @@
 from .base import (Embedding, FeedForward, Head, Mixer, Norm, PagedCacheSpec, Part, PositionEncoding, StateSpec,
-                   build_embedding, build_feed_forward, build_head, build_mixer, build_norm, build_position,
+                   build_embedding, build_feed_forward, build_head, build_mixer, build_norm, build_position, build_reentry,
                    part_factory, register_part, register_step_layout, unregister_part)
 from .linear import linear, prepare_weight
-from .norm import RMSNorm
+from .norm import DynamicTanh, RMSNorm
 from .rope import RotaryEncoding
 from .attention import Attention
-from .feed_forward import SwiGLU
-from .block import PreNormBlock, build_block
+from .feed_forward import ExpertMixture, SwiGLU
+from .sink_attention import SinkAttention
+from .gated_delta import GatedDeltaRule
+from .branches import BranchMixer
+from .reentry import ConcatReentry
+from .block import ParallelBlock, PreNormBlock, build_block
 from .embedding import TableEmbedding
 from .head import LinearHead
 
@@ -14,5 +18,6 @@ __all__ = [
     "Embedding", "Head", "build_embedding", "build_head", "TableEmbedding", "LinearHead", "FeedForward", "Mixer", "Norm", "PagedCacheSpec", "Part", "PositionEncoding", "StateSpec",
     "build_feed_forward", "build_mixer", "build_norm", "build_position", "part_factory",
     "register_part", "register_step_layout", "unregister_part", "linear", "RMSNorm", "RotaryEncoding", "Attention",
-    "SwiGLU", "PreNormBlock", "build_block",
+    "SwiGLU", "PreNormBlock", "build_block", "build_reentry", "DynamicTanh", "ExpertMixture", "SinkAttention",
+    "GatedDeltaRule", "BranchMixer", "ConcatReentry", "ParallelBlock",
 ]

@@ -44,6 +44,10 @@ class PagedCacheSpec:
     heads: int
     width: int
     window: int = 0
+    widths: Tuple[int, ...] = ()      # width of every entry where they differ (else `width` for all)
+
+    def entry_widths(self) -> Tuple[int, ...]:
+        return tuple(self.widths) if self.widths else (self.width,) * self.entries
 
 
 @dataclass(frozen=True)
@@ -156,6 +160,7 @@ class Head(Part):
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {
     "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "arrangement": {}, "embedding": {}, "head": {},
+    "reentry": {},
 }
 
 
@@ -177,7 +182,7 @@ def step_layout_providers() -> Dict[str, Callable]:
 
 def register_part(role: str, kind: str, factory: Callable, *, replace: bool = False) -> None:
     """Register `factory` for parts of `role` ('norm', 'position', 'mixer', 'feed_forward',
-    'arrangement', 'embedding', 'head') with the given kind."""
+    'arrangement', 'embedding', 'head', 'reentry') with the given kind."""
     if role not in _REGISTRIES:
         raise ConfigError(f"unknown part role '{role}'; roles: {sorted(_REGISTRIES)}")
     if kind in _REGISTRIES[role] and not replace:
@@ -220,6 +225,12 @@ def build_embedding(spec: PartSpec, hidden_size: int, vocab_size: int) -> Embedd
 
 def build_head(spec: PartSpec, hidden_size: int, vocab_size: int, tied: bool) -> Head:
     return part_factory("head", spec.kind)(spec, hidden_size, vocab_size, tied)
+
+
+def build_reentry(spec: Optional[PartSpec], hidden_size: int) -> Optional[Part]:
+    if spec is None:
+        return None
+    return part_factory("reentry", spec.kind)(spec, hidden_size)
 
 
 def build_feed_forward(spec: Optional[PartSpec], hidden_size: int) -> Optional[FeedForward]:

@@ -74,3 +74,67 @@ register_part("arrangement", "pre_norm", PreNormBlock, replace=True)
 
 def build_block(spec: LayerSpec, hidden_size: int):
     return part_factory("arrangement", spec.arrangement)(spec, hidden_size)
+
+
+class ParallelBlock:
+    """'parallel': one norm whose output both sublayers read, x <- x + (mixer(h) + ff(h)) with
+    h = norm(x), over a float32 residual stream (the norm is one that keeps the stream, like
+    `DynamicTanh`). The add is deferred like the pre-norm block's: a block receives the stream
+    and what the block before left to be added (`ops.DeferredSum`), its norm adds while it
+    reads, and it returns its own sublayers' outputs unadded. A block without a feed-forward
+    returns the mixer's output alone.
+
+    Checkpoint names: `LayerSpec.names` maps the roles "norm", "mixer", "feed_forward" to name
+    fragments; the norm's `weight` tensor is called by the fragment itself and its other tensors
+    `<fragment>.<key>`."""
+
+    def __init__(self, spec: LayerSpec, hidden_size: int):
+        self.spec = spec
+        if spec.position is not None:
+            raise ConfigError("parallel block: position encodings belong to the mixers that apply them")
+        self.mixer = build_mixer(spec.mixer, hidden_size, None)
+        self.feed_forward = build_feed_forward(spec.feed_forward, hidden_size)
+        self.norm = build_norm(spec.norm, hidden_size)
+        self.capture_safe = True
+
+    def _children(self):
+        n = self.spec.name_of
+        yield n("norm"), self.norm
+        yield n("mixer"), self.mixer
+        if self.feed_forward is not None:
+            yield n("feed_forward"), self.feed_forward
+
+    def _names(self):
+        """(checkpoint name relative to the layer, part, the part's key) for every tensor."""
+        n = self.spec.name_of
+        for key in self.norm.weight_specs():
+            yield (n("norm") if key == "weight" else f"{n('norm')}.{key}"), self.norm, key
+        for key in self.mixer.weight_specs():
+            yield f"{n('mixer')}.{key}", self.mixer, key
+        if self.feed_forward is not None:
+            for key in self.feed_forward.weight_specs():
+                yield f"{n('feed_forward')}.{key}", self.feed_forward, key
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {name: part.weight_specs()[key] for name, part, key in self._names()}
+
+    def load(self, tensors, dtype):
+        per_part = {}
+        for name, part, key in self._names():
+            if name in tensors:
+                per_part.setdefault(id(part), (part, {}))[1][key] = tensors[name]
+        for part, own in per_part.values():
+            part.load(own, dtype)
+
+    def setup(self, device, dtype):
+        for _, part in self._children():
+            part.setup(device, dtype)
+
+    def forward(self, ctx, hidden, residual, cache, writes_cache=True):
+        normed, residual = self.norm.forward_add(ctx, hidden, residual)
+        mixed = self.mixer.forward(ctx, normed, cache, writes_cache)
+        fed = self.feed_forward.forward(ctx, normed) if self.feed_forward is not None else None
+        return ops.DeferredSum(mixed, fed), residual
+
+
+register_part("arrangement", "parallel", ParallelBlock, replace=True)

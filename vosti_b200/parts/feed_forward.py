@@ -4,6 +4,13 @@ gate and up are one [2I, hidden] matrix (gate rows first) so that the projection
 single product, as the reference's loader concatenates them
 (python/vosti_kernels/model_families/qwen3/loader.py:55-58); the activation is
 gate * sigmoid(gate) * up in float32 (kernels/triton_kernels/silu_mul.py:66-87).
+
+Parameters besides `intermediate_size`: `tensor_names`, the checkpoint's names of the gate, up
+and down matrices (default: Qwen3's), and `float32_out`, for models whose residual stream is
+float32: the down projection is then not rounded to the serving type.
+
+`ExpertMixture` is the same feed-forward as `experts` small ones, of which each token uses
+the `top` with the largest router logits, weighted by the softmax over the chosen logits only.
 """
 from __future__ import annotations
 
@@ -18,45 +25,108 @@ from .base import FeedForward, register_part
 from .linear import linear, prepare_weight, uses_tensor_cores
 
 
+def stack_gate_up(gate: torch.Tensor, up: torch.Tensor, dtype: torch.dtype):
+    """One [2I, hidden] matrix for the gate and up projections, and whether SiLU(gate)*up can be
+    the tensor-core product's epilogue. If so, rows are laid out as blocks of 16 gate rows
+    followed by their 16 up rows, so that both halves of an output land in one warp's slice of
+    the accumulator; else the gate rows come first."""
+    inter = gate.shape[0]
+    common = torch.float32 if torch.float32 in (gate.dtype, up.dtype) else gate.dtype
+    stacked = torch.cat([gate.to(common), up.to(common)], dim=0)
+    fused = dtype == torch.bfloat16 and inter % 16 == 0 and uses_tensor_cores(dtype, stacked)
+    if not fused:
+        return stacked.contiguous(), False
+    h = stacked.shape[1]
+    blocks = torch.stack([stacked[:inter].view(-1, 16, h), stacked[inter:].view(-1, 16, h)], dim=1)
+    return prepare_weight(blocks.reshape(2 * inter, h).contiguous(), dtype), True
+
+
+def gated_activation(ctx, x, w_gate_up, fused: bool):
+    if fused:
+        return ops.gemm_tc(ops.materialize(x), w_gate_up, ctx.status, swiglu=True)
+    return ops.silu_mul(linear(ctx, x, w_gate_up))
+
+
 class SwiGLU(FeedForward):
     def __init__(self, spec: PartSpec, hidden_size: int):
         super().__init__(spec, hidden_size)
         self.inter = int(spec["intermediate_size"])
         if self.inter <= 0:
             raise ConfigError("swiglu: intermediate_size must be positive")
+        self.names = tuple(spec.get("tensor_names") or ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
+        self.float32_out = bool(spec.get("float32_out", False))
         self.w_gate_up = self.w_down = None
         self.fused = False
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         h, i = self.hidden_size, self.inter
-        return {"gate_proj.weight": WeightSpec((i, h)), "up_proj.weight": WeightSpec((i, h)),
-                "down_proj.weight": WeightSpec((h, i))}
+        gate, up, down = self.names
+        return {gate: WeightSpec((i, h)), up: WeightSpec((i, h)), down: WeightSpec((h, i))}
 
     def load(self, tensors, dtype):
-        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
-        common = torch.float32 if torch.float32 in (gate.dtype, up.dtype) else gate.dtype
-        self.w_down = prepare_weight(tensors["down_proj.weight"], dtype)
-        stacked = torch.cat([gate.to(common), up.to(common)], dim=0)
-        # On the tensor-core path SiLU(gate)*up is the product's epilogue: rows are laid out
-        # as blocks of 16 gate rows followed by their 16 up rows, so that both halves of an
-        # output land in one warp's slice of the accumulator.
-        self.fused = (dtype == torch.bfloat16 and self.inter % 16 == 0 and uses_tensor_cores(dtype, stacked))
-        if self.fused:
-            h = stacked.shape[1]
-            blocks = torch.stack([stacked[:self.inter].view(-1, 16, h), stacked[self.inter:].view(-1, 16, h)], dim=1)
-            self.w_gate_up = prepare_weight(blocks.reshape(2 * self.inter, h).contiguous(), dtype)
-        else:
-            self.w_gate_up = stacked.contiguous()
+        gate, up, down = self.names
+        self.w_down = prepare_weight(tensors[down], dtype)
+        self.w_gate_up, self.fused = stack_gate_up(tensors[gate], tensors[up], dtype)
 
     def first_weight(self):
         return self.w_gate_up
 
     def forward(self, ctx, x):
-        if self.fused:
-            mlp = ops.gemm_tc(ops.materialize(x), self.w_gate_up, ctx.status, swiglu=True)
-        else:
-            mlp = ops.silu_mul(linear(ctx, x, self.w_gate_up))
+        mlp = gated_activation(ctx, x, self.w_gate_up, self.fused)
+        if self.float32_out:
+            return linear(ctx, mlp, self.w_down, out_dtype=torch.float32)
         return linear(ctx, mlp, self.w_down, allow_partial=True)     # summed by the norm that follows
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)
+
+
+class ExpertMixture(FeedForward):
+    """Parameters: experts, top, intermediate_size (of one expert), `float32_out`. Tensors:
+    `router` [experts, hidden] and `e<i>.gate`, `e<i>.up`, `e<i>.down`.
+
+    The router's logits are float32. The experts' gate and up matrices stand side by side as one
+    [2 * experts * I, hidden] matrix and their down matrices as one [hidden, experts * I]: every
+    token's activation is computed for all experts by one product, each expert's slice is
+    multiplied by the token's weight for it (zero if it was not chosen), and one more product
+    sums the chosen experts' outputs. No launch depends on the router's choice, so a step may be
+    replayed from a CUDA graph."""
+
+    def __init__(self, spec: PartSpec, hidden_size: int):
+        super().__init__(spec, hidden_size)
+        self.experts, self.top = int(spec["experts"]), int(spec["top"])
+        self.inter = int(spec["intermediate_size"])
+        self.float32_out = bool(spec.get("float32_out", False))
+        if self.experts <= 0 or not 0 < self.top <= self.experts or self.inter <= 0:
+            raise ConfigError("moe: experts, top (at most experts) and intermediate_size must be positive")
+        self.router = self.w_gate_up = self.w_down = None
+        self.fused = False
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        h, i = self.hidden_size, self.inter
+        specs = {"router": WeightSpec((self.experts, h), std=0.5)}
+        for e in range(self.experts):
+            specs.update({f"e{e}.gate": WeightSpec((i, h)), f"e{e}.up": WeightSpec((i, h)), f"e{e}.down": WeightSpec((h, i))})
+        return specs
+
+    def load(self, tensors, dtype):
+        self.router = tensors["router"].float().contiguous()        # 32-bit logits from exact 32-bit products
+        gate = torch.cat([tensors[f"e{e}.gate"] for e in range(self.experts)], dim=0)
+        up = torch.cat([tensors[f"e{e}.up"] for e in range(self.experts)], dim=0)
+        self.w_gate_up, self.fused = stack_gate_up(gate, up, dtype)
+        self.w_down = prepare_weight(torch.cat([tensors[f"e{e}.down"] for e in range(self.experts)], dim=1).contiguous(), dtype)
+
+    def first_weight(self):
+        return self.w_gate_up
+
+    def forward(self, ctx, x):
+        x = ops.materialize(x)
+        logits = ops.gemm_simt(x, self.router, ctx.status, out_dtype=torch.float32)
+        _, _, dense = ops.moe_route(logits, self.top)
+        act = ops.moe_scale(gated_activation(ctx, x, self.w_gate_up, self.fused), dense, self.inter)
+        if self.float32_out:
+            return linear(ctx, act, self.w_down, out_dtype=torch.float32)
+        return linear(ctx, act, self.w_down, allow_partial=True)
+
+
+register_part("feed_forward", "moe", ExpertMixture, replace=True)

@@ -38,3 +38,47 @@ class RMSNorm(Norm):
 
 
 register_part("norm", "rmsnorm", RMSNorm, replace=True)
+
+
+class DynamicTanh(Norm):
+    """A norm that computes no statistics: tanh(alpha * x) * weight + bias with a learned scalar
+    alpha. It serves models whose residual stream is float32 in both serving types: `forward_add`
+    takes the stream and what is still to be added to it (a tensor or an `ops.DeferredSum`),
+    adds in float32, stores the sum as the new stream and returns the normed rows in the
+    serving type. Parameters: `bias` (default true) says whether a bias vector exists,
+    `bias_name` what the checkpoint calls it beside the weight (default "bias")."""
+
+    def __init__(self, spec: PartSpec, width: int):
+        super().__init__(spec, width)
+        self.width = width
+        self.has_bias = bool(spec.get("bias", True))
+        self.bias_key = str(spec.get("bias_name", "bias"))
+        self.weight = self.bias = None
+        self.alpha = 1.0
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        specs = {"weight": WeightSpec((self.width,), init="norm", std=0.1), "alpha": WeightSpec((), init="norm", std=0.1)}
+        if self.has_bias:
+            specs[self.bias_key] = WeightSpec((self.width,), std=0.1)
+        return specs
+
+    def load(self, tensors, dtype):
+        self.weight, self.bias = tensors["weight"], tensors.get(self.bias_key)
+        if self.bias is not None and self.bias.dtype != self.weight.dtype:
+            self.weight, self.bias = self.weight.float(), self.bias.float()
+        self.alpha = float(tensors["alpha"].float().item())
+        self.out_dtype = dtype
+
+    def forward(self, ctx, x):
+        return ops.dyt(x, self.weight, self.bias, self.alpha, ctx.dtype)
+
+    def forward_add(self, ctx, x, residual):
+        if residual is None:
+            # the stream starts here: the sum of what came is stored as float32
+            first = ops.materialize(x.terms[0] if isinstance(x, ops.DeferredSum) else x)
+            residual = torch.empty(first.shape, dtype=torch.float32, device=first.device)
+            return ops.dyt(x, self.weight, self.bias, self.alpha, ctx.dtype, stream_out=residual), residual
+        return ops.dyt(x, self.weight, self.bias, self.alpha, ctx.dtype, stream=residual, stream_out=residual), residual
+
+
+register_part("norm", "dyt", DynamicTanh, replace=True)

@@ -1,0 +1,109 @@
+"""Grouped-query attention without rotation whose key and value heads may differ in width,
+with three additions, each of them optional and a parameter of the spec:
+
+* `q_temp_coef`, `q_temp_every`: the query at position p is multiplied by
+  1 + coef * ln(floor((p + 1) / every) + 1) (long contexts sharpen their scores);
+* `bias_rows`, `bias_far`: a learned table `rel` [rows, heads] is added to the scaled score
+  by distance n = i - j: row n below rows // 2, then logarithmic steps,
+  min(rows - 1, half + floor(ln(n / half) / ln(far / half) * (rows - half))), which reach the
+  last row at distance `far`. The scale does not multiply the bias;
+* `sink`: a learned logit per head joins the softmax denominator once, with no key or value.
+
+Other parameters: num_heads, num_kv_heads (query head h reads kv head h // (heads / kv_heads)),
+head_dim, v_head_dim, scale, window (0: every earlier key). Keys and values live in the paged
+cache like those of `Attention`, in two tensors of their own widths.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from .. import ops
+from ..config.schema import ConfigError, PartSpec
+from ..weights.loader import WeightSpec
+from .base import Mixer, PagedCacheSpec, PositionEncoding, register_part
+from .linear import linear, prepare_weight
+
+LOG2E = 1.4426950408889634
+
+
+def distance_bucket(n: int, rows: int, far: int) -> int:
+    half = rows // 2
+    if n < half:
+        return n
+    return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+
+
+class SinkAttention(Mixer):
+    def __init__(self, spec: PartSpec, hidden_size: int, position: Optional[PositionEncoding]):
+        super().__init__(spec, hidden_size, position)
+        if position is not None:
+            raise ConfigError("sink_attention: this mixer applies no position encoding to q and k")
+        self.nq, self.nkv = int(spec["num_heads"]), int(spec["num_kv_heads"])
+        self.dk, self.dv = int(spec["head_dim"]), int(spec.get("v_head_dim") or spec["head_dim"])
+        self.scale = float(spec["scale"])
+        self.window = int(spec.get("window", 0) or 0)
+        self.temp_coef = float(spec.get("q_temp_coef", 0.0) or 0.0)
+        self.temp_every = int(spec.get("q_temp_every", 1) or 1)
+        self.bias_rows = int(spec.get("bias_rows", 0) or 0)
+        self.bias_far = int(spec.get("bias_far", 0) or 0)
+        self.has_sink = bool(spec.get("sink", False))
+        if self.nq <= 0 or self.nkv <= 0 or self.nq % self.nkv:
+            raise ConfigError(f"sink_attention: num_heads {self.nq} must be a positive multiple of num_kv_heads {self.nkv}")
+        if not 0 < self.dk <= 256 or not 0 < self.dv <= 256:
+            raise ConfigError("sink_attention: head widths must be between 1 and 256")
+        if self.window < 0 or self.temp_every <= 0:
+            raise ConfigError("sink_attention: window must be >= 0 and q_temp_every positive")
+        if self.bias_rows and (self.bias_rows < 2 or self.bias_far <= self.bias_rows // 2):
+            raise ConfigError("sink_attention: the bias table needs at least two rows and bias_far beyond half of them")
+        self.w_qkv = self.w_o = self.rel = self.sink = self.bias_table = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        h, nq, nkv, dk, dv = self.hidden_size, self.nq, self.nkv, self.dk, self.dv
+        specs = {"q": WeightSpec((nq * dk, h)), "k": WeightSpec((nkv * dk, h)), "v": WeightSpec((nkv * dv, h)),
+                 "o": WeightSpec((h, nq * dv))}
+        if self.bias_rows:
+            specs["rel"] = WeightSpec((self.bias_rows, nq), std=1.0)
+        if self.has_sink:
+            specs["sink"] = WeightSpec((nq,), std=1.0)
+        return specs
+
+    def load(self, tensors, dtype):
+        parts = [tensors["q"], tensors["k"], tensors["v"]]
+        common = torch.float32 if any(p.dtype == torch.float32 for p in parts) else parts[0].dtype
+        self.w_qkv = prepare_weight(torch.cat([p.to(common) for p in parts], dim=0).contiguous(), dtype)
+        self.w_o = prepare_weight(tensors["o"], dtype)
+        self.sink = tensors["sink"].float().contiguous() if self.has_sink else None
+        if self.bias_rows:
+            # by distance, up to the first one that reaches the table's last row: [heads, distances],
+            # in base-2 units because the kernels' softmax runs in base 2
+            rel = tensors["rel"].float()
+            rows = []
+            for n in range(self.bias_far + 1):
+                rows.append(distance_bucket(n, self.bias_rows, self.bias_far))
+                if rows[-1] == self.bias_rows - 1:
+                    break
+            index = torch.tensor(rows, dtype=torch.long, device=rel.device)
+            self.bias_table = (rel[index].T * LOG2E).contiguous()
+
+    def first_weight(self):
+        return self.w_qkv
+
+    def cache_spec(self) -> PagedCacheSpec:
+        return PagedCacheSpec(entries=2, heads=self.nkv, width=self.dk, window=self.window, widths=(self.dk, self.dv))
+
+    def forward(self, ctx, x, cache, writes_cache: bool = True):
+        group = ctx.group(cache.group)
+        qkv = linear(ctx, x, self.w_qkv)
+        q = ops.qkv_store(qkv, cache.k if writes_cache else None, cache.v if writes_cache else None, nq=self.nq,
+                          nkv=self.nkv, dk=self.dk, dv=self.dv, page_size=group.page_size, positions=ctx.positions,
+                          slot_mapping=group.slot_mapping, temp_coef=self.temp_coef, temp_every=self.temp_every,
+                          status=ctx.status)
+        attn = ops.attention_sink(ctx, q, cache.k, cache.v, group, nq=self.nq, nkv=self.nkv, dk=self.dk, dv=self.dv,
+                                  scale=self.scale, window=self.window, bias=self.bias_table, sink=self.sink)
+        return linear(ctx, attn, self.w_o, out_dtype=torch.float32)
+
+
+register_part("mixer", "sink_attention", SinkAttention, replace=True)

@@ -13,7 +13,7 @@ from __future__ import annotations
 import hashlib
 import json
 from pathlib import Path
-from typing import Dict, Mapping
+from typing import Dict, Mapping, Optional
 
 import torch
 
@@ -58,15 +58,16 @@ def draw_tensors(expected: Mapping[str, WeightSpec], seed: int, *,
 
 
 def write_random_model(model_dir: str | Path, config: Mapping, seed: int,
-                       dtype: torch.dtype = torch.bfloat16) -> Path:
+                       dtype: torch.dtype = torch.bfloat16, shapes: Optional[Mapping[str, tuple]] = None) -> Path:
     """Write config.json and model.safetensors for `config` (the architecture's own
-    config.json content) with weights drawn from `seed`."""
+    config.json content) with weights drawn from `seed`. `shapes` names the tensor shapes that
+    give sizes the architecture's config.json leaves to the checkpoint."""
     from ..config import model_spec_from_config
     from ..models import expected_weights
 
     root = Path(model_dir)
     root.mkdir(parents=True, exist_ok=True)
-    spec = model_spec_from_config(config)
+    spec = model_spec_from_config(config, shapes)
     tensors = draw_tensors(expected_weights(spec), seed, device="cpu", dtype=dtype)
     (root / "config.json").write_text(json.dumps(dict(config), indent=1, sort_keys=True))
     write_safetensors(root / "model.safetensors", tensors,
