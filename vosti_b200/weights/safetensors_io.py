@@ -106,7 +106,8 @@ def write_safetensors(path: str | Path, tensors: Dict[str, torch.Tensor],
         handle.write(blob)
         for name in ordered:
             t = tensors[name].detach().cpu().contiguous()
-            handle.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            # (a scalar has no axis to reinterpret as bytes: write it as a vector of one)
+            handle.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")
 
 
 def open_model_shards(model_dir: str | Path) -> Dict[str, SafetensorsFile]:
