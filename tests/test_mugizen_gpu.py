@@ -181,6 +181,38 @@ def test_a_far_key_that_stands_out_is_found(dtype, far_key):
     assert (got[T - 1, :dv] - x[far_key, :dv]).abs().max() < 0.2       # head 0 returns the marked key's value (about 1)
 
 
+@pytest.mark.parametrize("heads,kv,d", [(4, 2, 64), (8, 2, 128), (2, 2, 128)])
+def test_sink_attention_on_the_tensor_memory_kernel(heads, kv, d):
+    """bfloat16, equal key and value widths of 64 or 128: long rows run on the tensor-memory
+    kernel, short ones beside them on the CUDA cores with their keys cut into segments. The bias
+    changes within the first 90 positions back, so tiles near the diagonal look it up and tiles
+    beyond add its last value; two requests of one batch, one long and one short row."""
+    gen = torch.Generator().manual_seed(d + heads)
+    width, T = 96, 600
+    spec, block = attention_case(heads, kv, d, d, rows=12, far=90, coef=0.4, every=64, scale=d ** -0.5)
+    mixer = build_mixer(spec, width, None)
+    W = attention_weights(mixer, width, gen, spread=1.5)
+    give(mixer, W, torch.bfloat16)
+    harness = Harness([mixer.cache_spec()], [None], torch.bfloat16, num_pages=90, page_size=16)
+    xa, xb = rounded(T, width, gen=gen), rounded(300, width, gen=gen)
+    named = {"p." + k: v for k, v in W.items()}
+    want_a, want_b = plain.sink_attention(xa, named, "p.", block), plain.sink_attention(xb, named, "p.", block)
+    cache = harness.cache.layer_caches[0]
+    got_a, got_b, at_a, at_b = [], [], 0, 0
+    for na, nb in ((130, 1), (3, 200), (1, 1), (401, 2), (65, 96)):
+        ctx = harness.context([StepEntry("a", [0] * na), StepEntry("b", [0] * nb)])
+        x = torch.cat([xa[at_a:at_a + na], xb[at_b:at_b + nb]]).to(DEV, torch.bfloat16)
+        out = mixer.forward(ctx, x, cache).float().cpu()
+        got_a.append(out[:na])
+        got_b.append(out[na:])
+        at_a, at_b = at_a + na, at_b + nb
+    assert at_a == T and at_b == 300
+    for got, want in ((torch.cat(got_a), want_a), (torch.cat(got_b), want_b)):
+        err = (got - want).abs().max(-1).values / want.abs().max()
+        assert err.max() < 0.02, (float(err.max()), int(err.argmax()))
+    assert harness.status.item() == 0
+
+
 def test_a_sink_that_outweighs_every_key_silences_its_head():
     width, T, heads, dk = 48, 20, 3, 16
     gen = torch.Generator().manual_seed(9)
@@ -240,7 +272,7 @@ def test_gated_delta_in_portions_and_token_by_token(heads, kv, dk, dv, taps):
         got = run_in_portions(mixer, harness, x, sizes, torch.float32)
         assert torch.allclose(got, want, **F32), sizes
         state = harness.cache.layer_caches[0].state[harness.cache.slot("s")].cpu()
-        assert torch.allclose(state[: heads * dk * dv].view(heads, dk, dv), final, **F32)
+        assert torch.allclose(state[: heads * dk * dv].view(heads, dv, dk).transpose(1, 2), final, **F32)   # kept transposed
         assert harness.status.item() == 0
 
 

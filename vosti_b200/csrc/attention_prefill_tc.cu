@@ -54,14 +54,20 @@ template <int D> __host__ __device__ constexpr int kv_stages() { return D == 128
 // with the 128-byte swizzle.
 __device__ __forceinline__ uint32_t swizzled(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
 
-template <int D>
+// BIASED: the scaled score also gets bias[head][min(distance, bias_last)] (base-2 units; the
+// table's last column serves every larger distance, so a tile that lies wholly beyond it adds a
+// constant), and exp(sink[head]) joins the denominator once at the end (either may be null).
+// Without BIASED the arithmetic is what it was before the flag existed, bit for bit.
+template <int D, bool BIASED>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                             const int* __restrict__ row_list, const int* __restrict__ cu_q,
                             const int* __restrict__ kv_len, const int* __restrict__ block_table, int max_pages,
-                            int page_size, int page_shift, int num_pages, int nq, int nkv, float scale_log2,
-                            int window, unsigned* status) {
+                            int page_size, int page_shift, int num_pages, int nq, int nkv, float scale_log2_in,
+                            int window, const float* __restrict__ bias, int bias_last,
+                            const float* __restrict__ sink, unsigned* status) {
+  const float scale_log2 = BIASED ? 1.f : scale_log2_in;      // BIASED: scores are scaled where the bias is added
   constexpr int NB = D / 64;                          // 64-element blocks of the head size
   constexpr int STAGES = kv_stages<D>();
   constexpr int Q_BYTES = NB * ROWS * 128;            // one row tile of Q
@@ -149,6 +155,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     const uint32_t o_tmem = lane_base + PV_COL + wg * D;
+    const int head = g * group + r % group;
+    const float* bias_h = (BIASED && bias != nullptr) ? bias + (int64_t)head * (bias_last + 1) : nullptr;
 
     for (int t = 0; t < my_tiles && ok; ++t) {
       const int key0 = tile_begin + t * KT;
@@ -163,6 +171,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&s_empty[wg]));       // the scores are in registers
+      if (BIASED && valid) {
+        const int d0 = pos - key0;                               // key i of the tile is d0 - i positions back
+        if (bias_h == nullptr || d0 - (KT - 1) >= bias_last) {
+          const float far = bias_h != nullptr ? bias_h[bias_last] : 0.f;
+#pragma unroll
+          for (int i = 0; i < KT; ++i)
+            raw[i >> 5][i & 31] = __float_as_uint(fmaf(__uint_as_float(raw[i >> 5][i & 31]), scale_log2_in, far));
+        } else {
+#pragma unroll
+          for (int i = 0; i < KT; ++i) {
+            const int back = min(max(d0 - i, 0), bias_last);     // (keys ahead of the row are masked below)
+            raw[i >> 5][i & 31] = __float_as_uint(fmaf(__uint_as_float(raw[i >> 5][i & 31]), scale_log2_in, __ldg(bias_h + back)));
+          }
+        }
+      }
       const bool masked = key0 + KT - 1 > pos || key0 < kstart;
       // the maximum is exact in any order: four independent chains, scaled once at the end
       // (scale_log2 > 0, so max(s * scale) = max(s) * scale bit for bit)
@@ -250,6 +273,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       ok = mbar_wait(smem_u32(&p_empty[wg][(my_tiles - 1) & 1]), ((my_tiles - 1) >> 1) & 1, &abort_flag, status);
     tc_fence_after();
     if (my_tiles > 0) {
+      if (BIASED && sink != nullptr && valid && m_run > -INFINITY) l_run += fast_exp2(sink[head] * LOG2E - m_run);
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       bf16* dst = out + ((int64_t)(q_start + token) * nq + g * group + r % group) * D;
 #pragma unroll 1
@@ -413,12 +437,12 @@ VOSTI_API int vosti_attention_prefill_tc_supported(int d, int page_size) {
   return (d == 64 || d == 128) && page_size > 0 && page_size % GROUP_KEYS == 0;
 }
 
-// Arguments and meaning as vosti_attention_prefill, plus the number of rows of q
-// (tokens_total); d must be 64 or 128 and page_size a multiple of 16.
-VOSTI_API int vosti_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
+namespace {
+int launch_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
                                          const int* row_list, int count, const int* cu_q, const int* kv_len,
                                          const int* block_table, int max_pages, int page_size, int num_pages, int nq,
                                          int nkv, int d, int max_q_len, int tokens_total, float scale, int window,
+                                         bool biased, const float* bias, int bias_last, const float* sink,
                                          unsigned* status, cudaStream_t stream) {
   VOSTI_REQUIRE(count >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention_prefill_tc: bad head counts nq=%d nkv=%d", nq, nkv);
   VOSTI_REQUIRE(nq / nkv <= 16, "attention_prefill_tc: at most 16 query heads per kv head, got %d", nq / nkv);
@@ -446,20 +470,52 @@ VOSTI_API int vosti_attention_prefill_tc(const void* q, const void* k_cache, con
   int page_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
-#define LAUNCH_PREFILL_TC(D)                                                                                         \
+#define LAUNCH_PREFILL_TC(D, B)                                                                                      \
   do {                                                                                                               \
     static bool configured = false;                                                                                  \
     if (!configured) {                                                                                               \
-      cudaFuncSetAttribute(attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
+      cudaFuncSetAttribute(attention_prefill_tc_kernel<D, B>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
                            (int)prefill_tc_smem_bytes<D>());                                                         \
       configured = true;                                                                                             \
     }                                                                                                                \
-    vosti_launch(attention_prefill_tc_kernel<D>, grid, dim3(THREADS), prefill_tc_smem_bytes<D>(), stream, map_q,     \
+    vosti_launch(attention_prefill_tc_kernel<D, B>, grid, dim3(THREADS), prefill_tc_smem_bytes<D>(), stream, map_q,  \
         map_k, map_v, (bf16*)out, row_list, cu_q, kv_len, block_table, max_pages, page_size, page_shift, num_pages,   \
-        nq, nkv, scale * LOG2E, window, status);                                                                      \
+        nq, nkv, scale * LOG2E, window, bias, bias_last, sink, status);                                               \
   } while (0)
-  if (d == 64) LAUNCH_PREFILL_TC(64);
-  else LAUNCH_PREFILL_TC(128);
+  if (biased) {
+    if (d == 64) LAUNCH_PREFILL_TC(64, true);
+    else LAUNCH_PREFILL_TC(128, true);
+  } else {
+    if (d == 64) LAUNCH_PREFILL_TC(64, false);
+    else LAUNCH_PREFILL_TC(128, false);
+  }
 #undef LAUNCH_PREFILL_TC
   VOSTI_LAUNCH_CHECK();
+}
+}  // namespace
+
+// Arguments and meaning as vosti_attention_prefill, plus the number of rows of q
+// (tokens_total); d must be 64 or 128 and page_size a multiple of 16.
+VOSTI_API int vosti_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                         const int* row_list, int count, const int* cu_q, const int* kv_len,
+                                         const int* block_table, int max_pages, int page_size, int num_pages, int nq,
+                                         int nkv, int d, int max_q_len, int tokens_total, float scale, int window,
+                                         unsigned* status, cudaStream_t stream) {
+  return launch_prefill_tc(q, k_cache, v_cache, out, row_list, count, cu_q, kv_len, block_table, max_pages, page_size,
+                           num_pages, nq, nkv, d, max_q_len, tokens_total, scale, window, false, nullptr, 0, nullptr,
+                           status, stream);
+}
+
+// The same with a distance bias (float32 [nq, bias_last + 1], base-2 units, or null) and a sink
+// logit per head (float32 [nq], natural units, or null): see attention_sink.cu for their meaning.
+VOSTI_API int vosti_attention_prefill_tc_biased(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                                const int* row_list, int count, const int* cu_q, const int* kv_len,
+                                                const int* block_table, int max_pages, int page_size, int num_pages,
+                                                int nq, int nkv, int d, int max_q_len, int tokens_total, float scale,
+                                                int window, const float* bias, int bias_last, const float* sink,
+                                                unsigned* status, cudaStream_t stream) {
+  VOSTI_REQUIRE(bias == nullptr || bias_last >= 0, "attention_prefill_tc: bad bias table");
+  return launch_prefill_tc(q, k_cache, v_cache, out, row_list, count, cu_q, kv_len, block_table, max_pages, page_size,
+                           num_pages, nq, nkv, d, max_q_len, tokens_total, scale, window, true, bias, bias_last, sink,
+                           status, stream);
 }

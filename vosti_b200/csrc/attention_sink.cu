@@ -7,17 +7,57 @@
 //     longer changes, so the table is as long as the distances that differ;
 //   * a sink: one more term exp(sink[head]) in the softmax denominator, with no key or value.
 //
-// Two kernels: the projection's post-pass (temperature, keys and values into their cache
-// slots) and the attention itself on the CUDA cores, one warp per (query token, query head),
-// float32 arithmetic for both storage types. A tile is 32 keys aligned to the absolute key
-// index, so a row's order of arithmetic depends on its position only, not on how the prompt
-// was cut or what else is in the batch.
+// Kernels: the projection's post-pass (temperature, keys and values into their cache slots)
+// and the attention itself on the CUDA cores, one warp per (query token, query head), float32
+// arithmetic for both storage types. A tile is 32 keys aligned to the absolute key index, so a
+// row's order of arithmetic depends on its position only, not on how the prompt was cut or
+// what else is in the batch. With few query rows (decoding) the keys are cut into segments of
+// a fixed length, one warp per (token, head, segment), and a second kernel merges a row's
+// segments in order; the sink joins at the merge. (Head sizes 64 and 128 in bfloat16 take the
+// tensor-memory kernel of attention_prefill_tc.cu for their long rows instead.)
 #include "common.cuh"
 
 namespace {
 constexpr int WARPS = 4;
 constexpr int MAX_W = 256;          // widest key or value head
 constexpr float LOG2E = 1.4426950408889634f;
+
+// q . k for one key row; 16-byte loads when the row's width allows them.
+__device__ __forceinline__ float dot_key(const float* __restrict__ q, const float* __restrict__ k, int d) {
+  float s = 0.f;
+  int i = 0;
+  if (d % 4 == 0) {
+    const float4* k4 = reinterpret_cast<const float4*>(k);
+    for (; i < d; i += 4) {
+      const float4 v = k4[i >> 2];
+      s = fmaf(q[i], v.x, s);
+      s = fmaf(q[i + 1], v.y, s);
+      s = fmaf(q[i + 2], v.z, s);
+      s = fmaf(q[i + 3], v.w, s);
+    }
+  }
+  for (; i < d; ++i) s = fmaf(q[i], k[i], s);
+  return s;
+}
+__device__ __forceinline__ float dot_key(const float* __restrict__ q, const bf16* __restrict__ k, int d) {
+  float s = 0.f;
+  int i = 0;
+  if (d % 8 == 0) {
+    const uint4* k8 = reinterpret_cast<const uint4*>(k);
+    for (; i < d; i += 8) {
+      const uint4 raw = k8[i >> 3];
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(p[j]);
+        s = fmaf(q[i + 2 * j], f.x, s);
+        s = fmaf(q[i + 2 * j + 1], f.y, s);
+      }
+    }
+  }
+  for (; i < d; ++i) s = fmaf(q[i], __bfloat162float(k[i]), s);
+  return s;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -53,16 +93,18 @@ template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                       T* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ request_of,
-                      const int* __restrict__ block_table, int max_pages, int page_size, int num_pages, int tokens,
+                      const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
+                      const int* __restrict__ token_list, int tokens,
                       int nq, int nkv, int dk, int dv, float scale_log2, int window, const float* __restrict__ bias,
-                      int bias_last, const float* __restrict__ sink, unsigned* status) {
+                      int bias_last, const float* __restrict__ sink, float* __restrict__ partial, int segment,
+                      unsigned* status) {
   extern __shared__ float q_smem[];
   pdl_wait();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t wid = (int64_t)blockIdx.x * WARPS + warp;
   if (wid >= (int64_t)tokens * nq) return;
-  const int t = (int)(wid / nq), h = (int)(wid % nq);
+  const int t = token_list != nullptr ? token_list[wid / nq] : (int)(wid / nq), h = (int)(wid % nq);
   const int g = h / (nq / nkv);
   float* qs = q_smem + warp * dk;
   const T* qrow = q + ((int64_t)t * nq + h) * dk;
@@ -71,7 +113,12 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
 
   const int b = request_of[t];
   const int pos = positions[t];
-  const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  int kend = pos;                                   // inclusive
+  if (partial != nullptr) {                         // this warp's segment of the keys (segment: a multiple of 32)
+    kstart = max(kstart, (int)blockIdx.y * segment);
+    kend = min(kend, (int)(blockIdx.y + 1) * segment - 1);
+  }
   const int* table = block_table + (int64_t)b * max_pages;
   const float* bias_h = bias != nullptr ? bias + (int64_t)h * (bias_last + 1) : nullptr;
 
@@ -80,9 +127,9 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
 #pragma unroll
   for (int i = 0; i < MAX_W / 32; ++i) acc[i] = 0.f;
 
-  for (int j0 = (kstart / 32) * 32; j0 <= pos; j0 += 32) {
+  for (int j0 = (kstart / 32) * 32; j0 <= kend; j0 += 32) {
     const int j = j0 + lane;
-    bool valid = j >= kstart && j <= pos;
+    bool valid = j >= kstart && j <= kend;
     int64_t slot = 0;
     float s = -INFINITY;
     if (valid) {
@@ -93,10 +140,7 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
         valid = false;
       } else {
         slot = ((int64_t)page * nkv + g) * page_size + (j % page_size);   // row of (page, head, offset)
-        const T* krow = k_cache + slot * dk;
-        float dot = 0.f;
-        for (int i = 0; i < dk; ++i) dot = fmaf(qs[i], to_f32(krow[i]), dot);
-        s = dot * scale_log2;
+        s = dot_key(qs, k_cache + slot * dk, dk) * scale_log2;
         if (bias_h != nullptr) s += bias_h[min(pos - j, bias_last)];
       }
     }
@@ -108,7 +152,7 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
     l = l * alpha + warp_sum(p);
 #pragma unroll
     for (int i = 0; i < MAX_W / 32; ++i) acc[i] *= alpha;
-    const int last = min(31, pos - j0);
+    const int last = min(31, kend - j0);
     for (int kk = 0; kk <= last; ++kk) {
       const float pk = __shfl_sync(0xffffffffu, p, kk);
       const int64_t sk = __shfl_sync(0xffffffffu, slot, kk);
@@ -122,6 +166,20 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
     }
     m = m_new;
   }
+  if (partial != nullptr) {
+    // one record per (row, segment): maximum, sum, then the unnormalised values
+    float* rec = partial + (wid * gridDim.y + blockIdx.y) * (int64_t)(dv + 2);
+    if (lane == 0) {
+      rec[0] = m;
+      rec[1] = l;
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_W / 32; ++i) {
+      const int idx = lane + 32 * i;
+      if (idx < dv) rec[2 + idx] = acc[i];
+    }
+    return;
+  }
   if (sink != nullptr) {
     // the sink has a logit and nothing else: it joins the denominator once
     const float s = sink[h] * LOG2E;
@@ -130,6 +188,52 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
     l = l * alpha + exp2f(s - m_new);
 #pragma unroll
     for (int i = 0; i < MAX_W / 32; ++i) acc[i] *= alpha;
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  T* orow = out + ((int64_t)t * nq + h) * dv;
+#pragma unroll
+  for (int i = 0; i < MAX_W / 32; ++i) {
+    const int idx = lane + 32 * i;
+    if (idx < dv) orow[idx] = from_f32<T>(acc[i] * inv);
+  }
+}
+// A row's segments in segment order, then the sink, then the division.
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_sink_merge_kernel(const float* __restrict__ partial, int segments, T* __restrict__ out,
+                            const int* __restrict__ token_list, int tokens, int nq, int dv,
+                            const float* __restrict__ sink) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t wid = (int64_t)blockIdx.x * WARPS + warp;
+  if (wid >= (int64_t)tokens * nq) return;
+  const int t = token_list != nullptr ? token_list[wid / nq] : (int)(wid / nq), h = (int)(wid % nq);
+  float m = -INFINITY, l = 0.f;
+  float acc[MAX_W / 32];
+#pragma unroll
+  for (int i = 0; i < MAX_W / 32; ++i) acc[i] = 0.f;
+  for (int s = 0; s < segments; ++s) {
+    const float* rec = partial + (wid * segments + s) * (int64_t)(dv + 2);
+    const float ms = rec[0], ls = rec[1];
+    if (ms == -INFINITY) continue;
+    const float m_new = fmaxf(m, ms);
+    const float a = exp2f(m - m_new), c = exp2f(ms - m_new);
+    l = l * a + ls * c;
+#pragma unroll
+    for (int i = 0; i < MAX_W / 32; ++i) {
+      const int idx = lane + 32 * i;
+      if (idx < dv) acc[i] = acc[i] * a + rec[2 + idx] * c;
+    }
+    m = m_new;
+  }
+  if (sink != nullptr) {
+    const float s = sink[h] * LOG2E;
+    const float m_new = fmaxf(m, s);
+    const float a = exp2f(m - m_new);
+    l = l * a + exp2f(s - m_new);
+#pragma unroll
+    for (int i = 0; i < MAX_W / 32; ++i) acc[i] *= a;
   }
   const float inv = l > 0.f ? 1.f / l : 0.f;
   T* orow = out + ((int64_t)t * nq + h) * dv;
@@ -159,29 +263,49 @@ VOSTI_API int vosti_qkv_store(const void* qkv, void* q_out, void* k_cache, void*
   VOSTI_LAUNCH_CHECK();
 }
 
-// q: [tokens, nq, dk]; out: [tokens, nq, dv]; bias: float32 [nq, bias_last + 1] in natural-log units
-// times log2(e), or null; sink: float32 [nq] in natural-log units, or null.
+// q: [rows, nq, dk]; out: [rows, nq, dv]; bias: float32 [nq, bias_last + 1] in natural-log units
+// times log2(e), or null; sink: float32 [nq] in natural-log units, or null. `token_list` (or
+// null: all of them) names the `tokens` rows to compute. With `segments` > 1 the keys are cut
+// into pieces of `segment` keys (a multiple of 32) and `scratch` holds tokens * nq * segments *
+// (dv + 2) floats.
 VOSTI_API int vosti_attention_sink(const void* q, const void* k_cache, const void* v_cache, void* out, const int* positions,
                                    const int* request_of, const int* block_table, int max_pages, int page_size,
-                                   int num_pages, int tokens, int nq, int nkv, int dk, int dv, float scale, int window,
-                                   const float* bias, int bias_last, const float* sink, int is_f32, unsigned* status,
+                                   int num_pages, const int* token_list, int tokens, int nq, int nkv, int dk, int dv,
+                                   float scale, int window, const float* bias, int bias_last, const float* sink,
+                                   float* scratch, int segment, int segments, int is_f32, unsigned* status,
                                    cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention: bad head counts nq=%d nkv=%d", nq, nkv);
   VOSTI_REQUIRE(dk > 0 && dv > 0 && dk <= MAX_W && dv <= MAX_W, "attention: head widths %d / %d must be at most %d", dk, dv, MAX_W);
   VOSTI_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0, "attention: bad cache geometry");
   VOSTI_REQUIRE(window >= 0 && (bias == nullptr || bias_last >= 0), "attention: bad window or bias table");
+  VOSTI_REQUIRE(segments >= 1 && segments <= 65535 && (segments == 1 || (scratch != nullptr && segment > 0 && segment % 32 == 0)),
+                "attention: key segments need scratch and a length that is a multiple of 32");
   if (tokens == 0) return VOSTI_OK;
   const int64_t warps = (int64_t)tokens * nq;
   const int64_t blocks = (warps + WARPS - 1) / WARPS;
   VOSTI_REQUIRE(blocks <= 0x7fffffffLL, "attention: too many (token, head) pairs");
   const size_t smem = (size_t)WARPS * dk * sizeof(float);
+  float* partial = segments > 1 ? scratch : nullptr;
+  const dim3 grid((unsigned)blocks, segments > 1 ? segments : 1);
   if (is_f32)
-    vosti_launch(attention_sink_kernel<float>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, stream, (const float*)q,
+    vosti_launch(attention_sink_kernel<float>, grid, dim3(WARPS * 32), smem, stream, (const float*)q,
                  (const float*)k_cache, (const float*)v_cache, (float*)out, positions, request_of, block_table, max_pages,
-                 page_size, num_pages, tokens, nq, nkv, dk, dv, scale * LOG2E, window, bias, bias_last, sink, status);
+                 page_size, num_pages, token_list, tokens, nq, nkv, dk, dv, scale * LOG2E, window, bias, bias_last, sink,
+                 partial, segment, status);
   else
-    vosti_launch(attention_sink_kernel<bf16>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, stream, (const bf16*)q,
+    vosti_launch(attention_sink_kernel<bf16>, grid, dim3(WARPS * 32), smem, stream, (const bf16*)q,
                  (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions, request_of, block_table, max_pages,
-                 page_size, num_pages, tokens, nq, nkv, dk, dv, scale * LOG2E, window, bias, bias_last, sink, status);
+                 page_size, num_pages, token_list, tokens, nq, nkv, dk, dv, scale * LOG2E, window, bias, bias_last, sink,
+                 partial, segment, status);
+  if (segments > 1) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { vosti_set_error("%s", cudaGetErrorString(e)); return (int)e; }
+    if (is_f32)
+      vosti_launch(attention_sink_merge_kernel<float>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
+                   (const float*)partial, segments, (float*)out, token_list, tokens, nq, dv, sink);
+    else
+      vosti_launch(attention_sink_merge_kernel<bf16>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
+                   (const float*)partial, segments, (bf16*)out, token_list, tokens, nq, dv, sink);
+  }
   VOSTI_LAUNCH_CHECK();
 }

@@ -10,39 +10,41 @@
 // over the value channels, times a weight, times sigmoid(low-rank gate).
 //
 // Everything after the projections is float32 in both serving types. A request's state slot
-// is one float32 vector: S for every head [heads, dk, dv], then the convolution tail
-// [taps - 1, conv channels].
+// is one float32 vector: S for every head, stored transposed [heads, dv, dk] so that the key
+// channels a lane keeps are contiguous, then the convolution tail [taps - 1, conv channels].
 //
 // Kernels:
 //   delta_prep     one block per token: convolutions, unit vectors, beta, decay, gate
 //   delta_conv     one block per request: the convolution tail after this step
-//   delta_scan     one block per (request, head, 32 value columns): the recurrence over the
-//                  request's tokens of this step, from and to the state slot. Columns of S are
-//                  independent; a column's dk entries are spread over KS lanes of a warp.
+//   delta_scan     one block per (request, head, block of value columns): the recurrence over
+//                  the request's tokens of this step, from and to the state slot. Columns of S
+//                  are independent; a column's dk entries are spread over KS lanes of a warp,
+//                  8 contiguous ones to a lane, and the two sums over them are shuffles.
 //   delta_out      one warp per (token, head): the output stage
 #include "common.cuh"
 
 namespace {
 
 constexpr int MAX_TAPS = 16;
-constexpr int COLS = 32;        // value columns per block of the scan
-constexpr int ROWS = 32;        // key channels a lane keeps at most
+constexpr int SCAN_THREADS = 256;
+constexpr int ROWS = 8;         // key channels a lane keeps
 constexpr int TOKENS = 8;       // tokens staged in shared memory at a time
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
 __device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 struct PrepArgs {
-  // the fused projection [tokens, stride]: columns q | k | v | beta | decay low-rank | gate low-rank
+  // the fused projection [tokens, stride]: columns q | k | v | beta
   const void* proj;
   int proj_f32, stride;
-  int off_q, off_k, off_v, off_beta, off_a, off_g;
-  int kv_heads, heads, dk, dv, taps, rank_a, rank_g;
+  int off_q, off_k, off_v, off_beta;
+  // the low-rank pairs' products [tokens, heads dk + heads dv]: decay rates | output gates
+  const void* rates;
+  int rates_f32;
+  int kv_heads, heads, dk, dv, taps;
   const void* conv_w;           // [(2 kv_heads dk + heads dv), taps], the last column is the current token's
   const void* a_log;            // [heads]
   const void* dt_bias;          // [heads dk]
-  const void* a2;               // [heads dk, rank_a]
-  const void* g2;               // [heads dv, rank_g]
   int w_f32;
   const float* state;           // [slots, state_stride]
   int64_t state_stride, conv_offset;
@@ -61,7 +63,6 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(PrepArgs a) {
   const int t = blockIdx.x;
   const int cq = a.kv_heads * a.dk, cv = a.heads * a.dv, cc = 2 * cq + cv;
   float* y = smem;                        // [cc] convolved and activated q | k | v
-  float* low = smem + cc;                 // [rank_a + rank_g]
   const int b = a.request_of[t];
   const int local = t - a.cu_q[b];
   int slot = a.state_slots[b];
@@ -83,8 +84,6 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(PrepArgs a) {
     }
     y[c] = acc * sigmoidf_(acc);
   }
-  for (int r = threadIdx.x; r < a.rank_a + a.rank_g; r += blockDim.x)
-    low[r] = load_flex(a.proj, a.proj_f32, row + (r < a.rank_a ? a.off_a + r : a.off_g + (r - a.rank_a)));
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   // unit vectors: one warp per q or k head
@@ -102,17 +101,14 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(PrepArgs a) {
   for (int h = threadIdx.x; h < a.heads; h += blockDim.x)
     a.beta[(int64_t)t * a.heads + h] = sigmoidf_(load_flex(a.proj, a.proj_f32, row + a.off_beta + h));
   const int cd = a.heads * a.dk;
+  const int64_t rrow = (int64_t)t * (cd + cv);
   for (int c = threadIdx.x; c < cd; c += blockDim.x) {
-    float rate = load_flex(a.dt_bias, a.w_f32, c);
-    for (int r = 0; r < a.rank_a; ++r) rate = fmaf(load_flex(a.a2, a.w_f32, (int64_t)c * a.rank_a + r), low[r], rate);
+    const float rate = load_flex(a.rates, a.rates_f32, rrow + c) + load_flex(a.dt_bias, a.w_f32, c);
     const float speed = expf(load_flex(a.a_log, a.w_f32, c / a.dk));
     a.decay[(int64_t)t * cd + c] = expf(-speed * softplusf_(rate));
   }
-  for (int c = threadIdx.x; c < cv; c += blockDim.x) {
-    float z = 0.f;
-    for (int r = 0; r < a.rank_g; ++r) z = fmaf(load_flex(a.g2, a.w_f32, (int64_t)c * a.rank_g + r), low[a.rank_a + r], z);
-    a.gate[(int64_t)t * cv + c] = sigmoidf_(z);
-  }
+  for (int c = threadIdx.x; c < cv; c += blockDim.x)
+    a.gate[(int64_t)t * cv + c] = sigmoidf_(load_flex(a.rates, a.rates_f32, rrow + cd + c));
 }
 
 // The convolution tail of every request after this step: the last taps - 1 rows of
@@ -139,14 +135,19 @@ delta_conv_kernel(const void* proj, int proj_f32, int stride, int off_q, int cc,
   }
 }
 
-// KS lanes share a column; lane part `ks` keeps rows ks, ks + KS, ... of it.
+// KS lanes of a warp share a value column; lane part `ks` keeps key channels ks * 8 .. ks * 8 + 7
+// of it. A warp holds 32 / KS columns, a block SCAN_THREADS / KS. The staged rows of k, q and g
+// are padded with zeros to KS * 8 channels, so a lane reads its eight as two 16-byte words.
 template <int KS>
-__global__ void __launch_bounds__(COLS * KS)
+__global__ void __launch_bounds__(SCAN_THREADS)
 delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ out,
                   float* state, int64_t state_stride, const int* __restrict__ cu_q, const int* __restrict__ state_slots,
                   int num_slots, int kv_heads, int heads, int dk, int dv) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
+  constexpr int COLS = SCAN_THREADS / KS;       // value columns of a block
+  constexpr int PER_WARP = 32 / KS;             // columns of a warp
+  constexpr int PAD = KS * ROWS;                // staged channels per token
   pdl_wait();
   pdl_launch_dependents();
   const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
@@ -154,72 +155,85 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
   if (slot < 0 || slot >= num_slots) return;
   const int start = cu_q[b], n = cu_q[b + 1] - start;
   const int g = h / (heads / kv_heads);
-  const int ks = threadIdx.x % KS, col = col0 + threadIdx.x / KS;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ks = lane / PER_WARP, local = warp * PER_WARP + lane % PER_WARP, col = col0 + local;
   const bool live = col < dv;
-  float* S = state + (int64_t)slot * state_stride + (int64_t)h * dk * dv;
+  const int r0 = ks * ROWS;
+  float* S = state + (int64_t)slot * state_stride + ((int64_t)h * dv + col) * dk;     // this column's dk channels
   float s[ROWS];
+  const bool wide = (dk % 4 == 0) && live && r0 + ROWS <= dk;
+  if (wide) {
+    const float4 lo = *reinterpret_cast<const float4*>(S + r0), hi = *reinterpret_cast<const float4*>(S + r0 + 4);
+    s[0] = lo.x; s[1] = lo.y; s[2] = lo.z; s[3] = lo.w; s[4] = hi.x; s[5] = hi.y; s[6] = hi.z; s[7] = hi.w;
+  } else {
 #pragma unroll
-  for (int i = 0; i < ROWS; ++i) {
-    const int r = ks + i * KS;
-    s[i] = (live && r < dk) ? S[(int64_t)r * dv + col] : 0.f;
+    for (int i = 0; i < ROWS; ++i) s[i] = (live && r0 + i < dk) ? S[r0 + i] : 0.f;
   }
-  float* sk = smem;                       // [TOKENS][dk]
-  float* sq = sk + TOKENS * dk;
-  float* sg = sq + TOKENS * dk;
-  float* sv = sg + TOKENS * dk;           // [TOKENS][COLS]
+  float* sk = smem;                       // [TOKENS][PAD]
+  float* sq = sk + TOKENS * PAD;
+  float* sg = sq + TOKENS * PAD;
+  float* sv = sg + TOKENS * PAD;          // [TOKENS][COLS]
   float* sb = sv + TOKENS * COLS;         // [TOKENS]
   const int cq = kv_heads * dk, cd = heads * dk, cv = heads * dv;
   for (int t0 = 0; t0 < n; t0 += TOKENS) {
     const int count = min(TOKENS, n - t0);
     __syncthreads();
-    for (int i = threadIdx.x; i < count * dk; i += blockDim.x) {
-      const int64_t t = start + t0 + i / dk;
-      const int c = i % dk;
-      sk[i] = k[t * cq + g * dk + c];
-      sq[i] = q[t * cq + g * dk + c];
-      sg[i] = decay[t * cd + h * dk + c];
+    for (int i = threadIdx.x; i < count * PAD; i += SCAN_THREADS) {
+      const int64_t t = start + t0 + i / PAD;
+      const int c = i % PAD;
+      const bool in = c < dk;
+      sk[i] = in ? k[t * cq + g * dk + c] : 0.f;
+      sq[i] = in ? q[t * cq + g * dk + c] : 0.f;
+      sg[i] = in ? decay[t * cd + h * dk + c] : 0.f;
     }
-    for (int i = threadIdx.x; i < count * COLS; i += blockDim.x) {
+    for (int i = threadIdx.x; i < count * COLS; i += SCAN_THREADS) {
       const int64_t t = start + t0 + i / COLS;
       const int c = col0 + i % COLS;
       sv[i] = c < dv ? v[t * cv + h * dv + c] : 0.f;
     }
-    for (int i = threadIdx.x; i < count; i += blockDim.x) sb[i] = beta[(int64_t)(start + t0 + i) * heads + h];
+    for (int i = threadIdx.x; i < count; i += SCAN_THREADS) sb[i] = beta[(int64_t)(start + t0 + i) * heads + h];
     __syncthreads();
     for (int tt = 0; tt < count; ++tt) {
-      const float* kt = sk + tt * dk;
-      const float* qt = sq + tt * dk;
-      const float* gt = sg + tt * dk;
-      float dot = 0.f;
+      float kt[ROWS], qt[ROWS], gt[ROWS];
+      *reinterpret_cast<float4*>(kt) = *reinterpret_cast<const float4*>(sk + tt * PAD + r0);
+      *reinterpret_cast<float4*>(kt + 4) = *reinterpret_cast<const float4*>(sk + tt * PAD + r0 + 4);
+      *reinterpret_cast<float4*>(gt) = *reinterpret_cast<const float4*>(sg + tt * PAD + r0);
+      *reinterpret_cast<float4*>(gt + 4) = *reinterpret_cast<const float4*>(sg + tt * PAD + r0 + 4);
+      *reinterpret_cast<float4*>(qt) = *reinterpret_cast<const float4*>(sq + tt * PAD + r0);
+      *reinterpret_cast<float4*>(qt + 4) = *reinterpret_cast<const float4*>(sq + tt * PAD + r0 + 4);
+      float d0 = 0.f, d1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < ROWS; ++i) {
-        const int r = ks + i * KS;
-        if (r < dk) {
-          s[i] *= gt[r];
-          dot = fmaf(s[i], kt[r], dot);
-        }
+      for (int i = 0; i < ROWS; i += 2) {
+        s[i] *= gt[i];
+        s[i + 1] *= gt[i + 1];
+        d0 = fmaf(s[i], kt[i], d0);
+        d1 = fmaf(s[i + 1], kt[i + 1], d1);
       }
+      float dot = d0 + d1;
 #pragma unroll
-      for (int o = KS / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float u = sb[tt] * (sv[tt * COLS + threadIdx.x / KS] - dot);
-      float read = 0.f;
+      for (int o = PER_WARP; o < 32; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float u = sb[tt] * (sv[tt * COLS + local] - dot);
+      float e0 = 0.f, e1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < ROWS; ++i) {
-        const int r = ks + i * KS;
-        if (r < dk) {
-          s[i] = fmaf(kt[r], u, s[i]);
-          read = fmaf(s[i], qt[r], read);
-        }
+      for (int i = 0; i < ROWS; i += 2) {
+        s[i] = fmaf(kt[i], u, s[i]);
+        s[i + 1] = fmaf(kt[i + 1], u, s[i + 1]);
+        e0 = fmaf(s[i], qt[i], e0);
+        e1 = fmaf(s[i + 1], qt[i + 1], e1);
       }
+      float read = e0 + e1;
 #pragma unroll
-      for (int o = KS / 2; o > 0; o >>= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
+      for (int o = PER_WARP; o < 32; o <<= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
       if (ks == 0 && live) out[(int64_t)(start + t0 + tt) * cv + h * dv + col] = read;
     }
   }
+  if (wide) {
+    *reinterpret_cast<float4*>(S + r0) = make_float4(s[0], s[1], s[2], s[3]);
+    *reinterpret_cast<float4*>(S + r0 + 4) = make_float4(s[4], s[5], s[6], s[7]);
+  } else {
 #pragma unroll
-  for (int i = 0; i < ROWS; ++i) {
-    const int r = ks + i * KS;
-    if (live && r < dk) S[(int64_t)r * dv + col] = s[i];
+    for (int i = 0; i < ROWS; ++i)
+      if (live && r0 + i < dk) S[r0 + i] = s[i];
   }
 }
 
@@ -245,26 +259,26 @@ delta_out_kernel(const float* __restrict__ o, const float* __restrict__ gate, co
 }  // namespace
 
 VOSTI_API int vosti_delta_prep(const void* proj, int proj_f32, int stride, int off_q, int off_k, int off_v, int off_beta,
-                               int off_a, int off_g, int kv_heads, int heads, int dk, int dv, int taps, int rank_a,
-                               int rank_g, const void* conv_w, const void* a_log, const void* dt_bias, const void* a2,
-                               const void* g2, int w_f32, float* state, int64_t state_stride, int64_t conv_offset,
-                               const int* request_of, const int* cu_q, const int* state_slots, int num_slots,
-                               int requests, int tokens, float* q, float* k, float* v, float* beta, float* decay,
-                               float* gate, unsigned* status, cudaStream_t stream) {
+                               const void* rates, int rates_f32, int kv_heads, int heads, int dk, int dv, int taps,
+                               const void* conv_w, const void* a_log, const void* dt_bias, int w_f32, float* state,
+                               int64_t state_stride, int64_t conv_offset, const int* request_of, const int* cu_q,
+                               const int* state_slots, int num_slots, int requests, int tokens, float* q, float* k,
+                               float* v, float* beta, float* decay, float* gate, unsigned* status, cudaStream_t stream) {
   VOSTI_REQUIRE(kv_heads > 0 && heads > 0 && heads % kv_heads == 0 && dk > 0 && dv > 0, "delta_prep: bad head sizes");
   VOSTI_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "delta_prep: %d taps (1 to %d are taken)", taps, MAX_TAPS);
   VOSTI_REQUIRE(off_k == off_q + kv_heads * dk && off_v == off_k + kv_heads * dk, "delta_prep: q, k, v must be adjacent columns");
   if (tokens == 0) return VOSTI_OK;
   PrepArgs a = {};
   a.proj = proj; a.proj_f32 = proj_f32; a.stride = stride;
-  a.off_q = off_q; a.off_k = off_k; a.off_v = off_v; a.off_beta = off_beta; a.off_a = off_a; a.off_g = off_g;
-  a.kv_heads = kv_heads; a.heads = heads; a.dk = dk; a.dv = dv; a.taps = taps; a.rank_a = rank_a; a.rank_g = rank_g;
-  a.conv_w = conv_w; a.a_log = a_log; a.dt_bias = dt_bias; a.a2 = a2; a.g2 = g2; a.w_f32 = w_f32;
+  a.off_q = off_q; a.off_k = off_k; a.off_v = off_v; a.off_beta = off_beta;
+  a.rates = rates; a.rates_f32 = rates_f32;
+  a.kv_heads = kv_heads; a.heads = heads; a.dk = dk; a.dv = dv; a.taps = taps;
+  a.conv_w = conv_w; a.a_log = a_log; a.dt_bias = dt_bias; a.w_f32 = w_f32;
   a.state = state; a.state_stride = state_stride; a.conv_offset = conv_offset;
   a.request_of = request_of; a.cu_q = cu_q; a.state_slots = state_slots; a.num_slots = num_slots;
   a.q = q; a.k = k; a.v = v; a.beta = beta; a.decay = decay; a.gate = gate; a.status = status;
   const int cc = 2 * kv_heads * dk + heads * dv;
-  const size_t smem = (size_t)(cc + rank_a + rank_g) * sizeof(float);
+  const size_t smem = (size_t)cc * sizeof(float);
   VOSTI_REQUIRE(smem <= 200 * 1024, "delta_prep: %d channels do not fit shared memory", cc);
   if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   vosti_launch(delta_prep_kernel, dim3(tokens), dim3(256), smem, stream, a);
@@ -281,19 +295,27 @@ VOSTI_API int vosti_delta_scan(const float* q, const float* k, const float* v, c
                                float* out, float* state, int64_t state_stride, const int* cu_q, const int* state_slots,
                                int num_slots, int requests, int kv_heads, int heads, int dk, int dv, cudaStream_t stream) {
   VOSTI_REQUIRE(kv_heads > 0 && heads > 0 && heads % kv_heads == 0 && dk > 0 && dv > 0, "delta_scan: bad head sizes");
-  VOSTI_REQUIRE(dk <= ROWS * 8, "delta_scan: %d key channels (at most %d are taken)", dk, ROWS * 8);
-  VOSTI_REQUIRE(heads <= 65535 && (dv + COLS - 1) / COLS <= 65535, "delta_scan: too many heads or value channels");
+  VOSTI_REQUIRE(dk <= ROWS * 32, "delta_scan: %d key channels (at most %d are taken)", dk, ROWS * 32);
+  VOSTI_REQUIRE(heads <= 65535, "delta_scan: too many heads");
+  VOSTI_REQUIRE(state_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(state) & 15) == 0, "delta_scan: state slots must be 16-byte aligned");
   if (requests == 0) return VOSTI_OK;
-  const dim3 grid(requests, heads, (dv + COLS - 1) / COLS);
-  const size_t smem = (size_t)(TOKENS * (3 * dk + COLS) + TOKENS) * sizeof(float);
-  const int ks = dk <= ROWS ? 1 : dk <= 2 * ROWS ? 2 : dk <= 4 * ROWS ? 4 : 8;
+  int ks = 1;
+  while (ks * ROWS < dk) ks *= 2;
+  const int cols = SCAN_THREADS / ks;
+  VOSTI_REQUIRE((dv + cols - 1) / cols <= 65535, "delta_scan: too many value channels");
+  const dim3 grid(requests, heads, (dv + cols - 1) / cols);
+  const size_t smem = (size_t)(TOKENS * (3 * ks * ROWS + cols) + TOKENS) * sizeof(float);
 #define VOSTI_SCAN(KS)                                                                                              \
-  vosti_launch(delta_scan_kernel<KS>, grid, dim3(COLS * KS), smem, stream, q, k, v, beta, decay, out, state,       \
+  vosti_launch(delta_scan_kernel<KS>, grid, dim3(SCAN_THREADS), smem, stream, q, k, v, beta, decay, out, state,    \
                state_stride, cu_q, state_slots, num_slots, kv_heads, heads, dk, dv)
-  if (ks == 1) VOSTI_SCAN(1);
-  else if (ks == 2) VOSTI_SCAN(2);
-  else if (ks == 4) VOSTI_SCAN(4);
-  else VOSTI_SCAN(8);
+  switch (ks) {
+    case 1: VOSTI_SCAN(1); break;
+    case 2: VOSTI_SCAN(2); break;
+    case 4: VOSTI_SCAN(4); break;
+    case 8: VOSTI_SCAN(8); break;
+    case 16: VOSTI_SCAN(16); break;
+    default: VOSTI_SCAN(32); break;
+  }
 #undef VOSTI_SCAN
   VOSTI_LAUNCH_CHECK();
 }

@@ -17,12 +17,14 @@ import numpy as np
 from .batch import StepEntry
 from .runner import ModelRunner
 
-MAX_LIVE = 4      # requests live at any time: state slots are used again by later requests
+MAX_LIVE = 8
 
 
 class TraceReplayer:
     def __init__(self, model_dir, *, dtype: str, out_dir, max_tokens: int, page_size: int = 16,
-                 device: str = "cuda:0", batch_invariant=False):
+                 device: str = "cuda:0", batch_invariant=False, max_live: int = MAX_LIVE):
+        """`max_live`: how many requests may be live at a time; the engine has that many state
+        slots, which later requests use again."""
         if dtype == "bfloat16":
             from .. import ops
             ops.set_invariance(batch_invariant)
@@ -30,7 +32,7 @@ class TraceReplayer:
         self.out_dir.mkdir(parents=True, exist_ok=True)
         num_pages = (max_tokens + page_size - 1) // page_size
         self.runner = ModelRunner(model_dir, dtype=dtype, device=device, num_pages=num_pages,
-                                  page_size=page_size, max_requests=MAX_LIVE, prefix_reuse=False)
+                                  page_size=page_size, max_requests=max_live, prefix_reuse=False)
 
     def run_line(self, record: Dict) -> object:
         step = record["step"]

@@ -745,44 +745,82 @@ def qkv_store(qkv: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optio
     return q
 
 
+SINK_SEGMENT = 256          # keys per segment when few query rows share the GPU
+SINK_SPLIT_MAX_ROWS = 2048  # (token, head) rows up to which the keys are cut into segments
+
+
+def _attention_sink_rows(ctx, q, k_cache, v_cache, out, group, *, token_list, count, nq, nkv, dk, dv, scale, window,
+                         bias, sink) -> None:
+    """The CUDA-core kernel over `count` rows of the step (all of them if `token_list` is None)."""
+    flag = _same_dtype(q, k_cache, v_cache)
+    num_pages = k_cache.numel() // (group.page_size * nkv * dk)
+    segments, scratch = 1, None
+    if count * nq <= SINK_SPLIT_MAX_ROWS and ctx.max_kv_len > SINK_SEGMENT:
+        segments = -(-ctx.max_kv_len // SINK_SEGMENT)
+        scratch = _workspace(q.device, count * nq * segments * (dv + 2))
+    _check(library().vosti_attention_sink(
+        _p(q), _p(k_cache), _p(v_cache), _p(out), _p(ctx.positions), _p(ctx.request_of), _p(group.block_table),
+        group.block_table.shape[1], group.page_size, num_pages, _p(token_list), count, nq, nkv, dk, dv,
+        ctypes.c_float(scale), window, _p(bias), 0 if bias is None else bias.shape[1] - 1, _p(sink), _p(scratch),
+        SINK_SEGMENT, segments, flag, _p(ctx.status), _stream()), "attention_sink", kernels=2 if segments > 1 else 1)
+
+
 def attention_sink(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, *, nq: int, nkv: int,
                    dk: int, dv: int, scale: float, window: int, bias: Optional[torch.Tensor],
                    sink: Optional[torch.Tensor]) -> torch.Tensor:
     """Causal attention of every query row over its request's cached keys, with an optional bias
     table float32 [nq, distances] (base-2 units, the last column serving every larger distance)
-    and an optional sink logit per head (float32 [nq], natural units). Returns [tokens, nq * dv]."""
+    and an optional sink logit per head (float32 [nq], natural units). Returns [tokens, nq * dv].
+    bfloat16 with equal key and value widths of 64 or 128 (pages of a multiple of 16 tokens, at
+    most 16 query heads per kv head): the step's long rows run on the tensor-memory kernel,
+    its short ones (the step's work lists: attention_step_layout) on the CUDA cores with the keys
+    cut into segments. Everything else runs on the CUDA-core kernel."""
     _contig(q, k_cache, v_cache, bias, sink)
-    flag = _same_dtype(q, k_cache, v_cache)
     tokens = q.shape[0]
     out = torch.empty((tokens, nq * dv), dtype=q.dtype, device=q.device)
+    common = dict(nq=nq, nkv=nkv, dk=dk, dv=dv, scale=scale, window=window, bias=bias, sink=sink)
+    lib = library()
+    lists = ctx.layout.get("attention") if getattr(ctx, "layout", None) else None
+    tensor_memory = (q.dtype == torch.bfloat16 and dk == dv and nq // nkv <= 16 and lists is not None
+                     and lists["num_long_rows"] > 0 and lib.vosti_attention_prefill_tc_supported(dk, group.page_size))
+    if not tensor_memory:
+        _attention_sink_rows(ctx, q, k_cache, v_cache, out, group, token_list=None, count=tokens, **common)
+        return out
+    if lists["num_short_tokens"]:
+        _attention_sink_rows(ctx, q, k_cache, v_cache, out, group, token_list=ctx.extras.get("attention.short_tokens"),
+                             count=lists["num_short_tokens"], **common)
     num_pages = k_cache.numel() // (group.page_size * nkv * dk)
-    _check(library().vosti_attention_sink(
-        _p(q), _p(k_cache), _p(v_cache), _p(out), _p(ctx.positions), _p(ctx.request_of), _p(group.block_table),
-        group.block_table.shape[1], group.page_size, num_pages, tokens, nq, nkv, dk, dv, ctypes.c_float(scale), window,
-        _p(bias), 0 if bias is None else bias.shape[1] - 1, _p(sink), flag, _p(ctx.status), _stream()), "attention_sink")
+    _check(lib.vosti_attention_prefill_tc_biased(
+        _p(q), _p(k_cache), _p(v_cache), _p(out), _p(ctx.extras.get("attention.long_rows")), lists["num_long_rows"],
+        _p(ctx.cu_q), _p(ctx.kv_len), _p(group.block_table), group.block_table.shape[1], group.page_size, num_pages, nq,
+        nkv, dk, lists["max_long_q_len"], tokens, ctypes.c_float(scale), window, _p(bias),
+        0 if bias is None else bias.shape[1] - 1, _p(sink), _p(ctx.status), _stream()), "attention_prefill_tc_biased")
     return out
 
 
 # ---------------------------------------------------------------- gated delta rule
-def delta_prep(proj: torch.Tensor, offsets: dict, *, kv_heads: int, heads: int, dk: int, dv: int, taps: int, rank_a: int,
-               rank_g: int, conv_w, a_log, dt_bias, a2, g2, state: torch.Tensor, conv_offset: int, ctx):
-    """Everything between the fused projection and the recurrence (see csrc/delta_rule.cu); also
-    moves the convolution tail in the requests' state slots on. Returns float32 q, k, v, beta,
-    decay, gate."""
-    proj = materialize(proj)
-    small = (conv_w, a_log, dt_bias, a2, g2)
-    _contig(proj, state, *small)
+def delta_prep(proj: torch.Tensor, rates: torch.Tensor, offsets: dict, *, kv_heads: int, heads: int, dk: int, dv: int,
+               taps: int, conv_w, a_log, dt_bias, state: torch.Tensor, conv_offset: int, ctx):
+    """Everything between the projections and the recurrence (see csrc/delta_rule.cu): `proj` holds
+    the columns q | k | v | beta at `offsets`, `rates` [tokens, heads*dk + heads*dv] the low-rank
+    pairs' products (decay rates, then output gates, before their activations). Also moves the
+    convolution tail in the requests' state slots on. Returns float32 q, k, v, beta, decay, gate."""
+    proj, rates = materialize(proj), materialize(rates)
+    small = (conv_w, a_log, dt_bias)
+    _contig(proj, rates, state, *small)
     flag = _is_f32(conv_w)
     if any(_is_f32(t) != flag for t in small) or state.dtype != torch.float32:
         raise KernelError("delta_prep: the small tensors must share a dtype and the state is float32")
     tokens, dev = proj.shape[0], proj.device
+    if tuple(rates.shape) != (tokens, heads * (dk + dv)):
+        raise KernelError("delta_prep: the rates do not match the head sizes")
     new = lambda width: torch.empty((tokens, width), dtype=torch.float32, device=dev)
     q, k, v = new(kv_heads * dk), new(kv_heads * dk), new(heads * dv)
     beta, decay, gate = new(heads), new(heads * dk), new(heads * dv)
     _check(library().vosti_delta_prep(
-        _p(proj), _is_f32(proj), proj.shape[1], offsets["q"], offsets["k"], offsets["v"], offsets["b"], offsets["a"],
-        offsets["g"], kv_heads, heads, dk, dv, taps, rank_a, rank_g, _p(conv_w), _p(a_log), _p(dt_bias), _p(a2), _p(g2),
-        flag, _p(state), ctypes.c_int64(state.shape[1]), ctypes.c_int64(conv_offset), _p(ctx.request_of), _p(ctx.cu_q),
+        _p(proj), _is_f32(proj), proj.shape[1], offsets["q"], offsets["k"], offsets["v"], offsets["b"], _p(rates),
+        _is_f32(rates), kv_heads, heads, dk, dv, taps, _p(conv_w), _p(a_log), _p(dt_bias), flag, _p(state),
+        ctypes.c_int64(state.shape[1]), ctypes.c_int64(conv_offset), _p(ctx.request_of), _p(ctx.cu_q),
         _p(ctx.state_slots), state.shape[0], ctx.num_requests, tokens, _p(q), _p(k), _p(v), _p(beta), _p(decay), _p(gate),
         _p(ctx.status), _stream()), "delta_prep", kernels=2 if taps > 1 else 1)
     return q, k, v, beta, decay, gate

@@ -12,10 +12,12 @@ g = exp(-exp(A_log) * softplus(W_a2 (W_a1 h) + dt_bias)); each head's o is divid
 mean square (`eps`), multiplied by a weight shared by the heads and by sigmoid(W_g2 (W_g1 h)),
 and projected by W_o. Everything after the projections is float32 in both serving types.
 
-The state slot of a request holds S for every head and the convolutions' last taps - 1
-inputs; the scheduler hands it out zeroed. All seven projections that read the layer's input
-are one product. The ranks of the two low-rank pairs come from the spec (`decay_rank`,
-`gate_rank`).
+The state slot of a request holds S for every head (transposed, [heads, v_head_dim,
+head_dim]) and the convolutions' last taps - 1 inputs; the scheduler hands it out zeroed.
+Three products feed the recurrence: q | k | v | beta in one, the first halves of the two
+low-rank pairs in one, and their second halves in one (a block-diagonal matrix, whose zeros
+add nothing); its result, the decay rates and gates before their activations, is float32. The
+ranks of the pairs come from the spec (`decay_rank`, `gate_rank`).
 """
 from __future__ import annotations
 
@@ -47,13 +49,13 @@ class GatedDeltaRule(Mixer):
         self.cq, self.cv = self.kv_heads * self.dk, self.heads * self.dv
         self.conv_channels = 2 * self.cq + self.cv
         self.conv_offset = self.heads * self.dk * self.dv
-        widths = [("q", self.cq), ("k", self.cq), ("v", self.cv), ("b", self.heads), ("a", self.rank_a), ("g", self.rank_g)]
+        widths = [("q", self.cq), ("k", self.cq), ("v", self.cv), ("b", self.heads)]
         self.offsets, at = {}, 0
         for name, width in widths:
             self.offsets[name] = at
             at += width
         self.proj_width = at
-        self.w_in = self.w_o = None
+        self.w_in = self.w_low = self.w_rates = self.w_o = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         h = self.hidden_size
@@ -70,31 +72,42 @@ class GatedDeltaRule(Mixer):
         }
 
     def load(self, tensors, dtype):
-        parts = [tensors[n] for n in ("q", "k", "v", "b", "a1", "g1")]
-        common = torch.float32 if any(p.dtype == torch.float32 for p in parts) else parts[0].dtype
-        self.w_in = prepare_weight(torch.cat([p.to(common) for p in parts], dim=0).contiguous(), dtype)
+        def stacked(names):
+            parts = [tensors[n] for n in names]
+            common = torch.float32 if any(p.dtype == torch.float32 for p in parts) else parts[0].dtype
+            return torch.cat([p.to(common) for p in parts], dim=0).contiguous()
+        self.w_in = prepare_weight(stacked(("q", "k", "v", "b")), dtype)
+        self.w_low = prepare_weight(stacked(("a1", "g1")), dtype)
+        a2, g2 = tensors["a2"], tensors["g2"]
+        common = torch.float32 if torch.float32 in (a2.dtype, g2.dtype) else a2.dtype
+        second = torch.zeros((a2.shape[0] + g2.shape[0], self.rank_a + self.rank_g), dtype=common, device=a2.device)
+        second[: a2.shape[0], : self.rank_a] = a2
+        second[a2.shape[0]:, self.rank_a:] = g2
+        self.w_rates = prepare_weight(second, dtype)
         self.w_o = prepare_weight(tensors["o"], dtype)
-        small = {n: tensors[n] for n in ("q.conv", "k.conv", "v.conv", "A_log", "dt_bias", "a2", "g2", "norm")}
+        small = {n: tensors[n] for n in ("q.conv", "k.conv", "v.conv", "A_log", "dt_bias", "norm")}
         if len({t.dtype for t in small.values()}) > 1:
             small = {n: t.float() for n, t in small.items()}
         self.conv_w = torch.cat([small["q.conv"], small["k.conv"], small["v.conv"]], dim=0).contiguous()
-        self.a_log, self.dt_bias, self.a2, self.g2 = small["A_log"], small["dt_bias"], small["a2"], small["g2"]
+        self.a_log, self.dt_bias = small["A_log"], small["dt_bias"]
         self.norm = small["norm"]
 
     def first_weight(self):
         return self.w_in
 
     def state_spec(self) -> StateSpec:
-        return StateSpec((self.conv_offset + (self.taps - 1) * self.conv_channels,), torch.float32)
+        size = self.conv_offset + (self.taps - 1) * self.conv_channels
+        return StateSpec(((size + 3) // 4 * 4,), torch.float32)          # slots start on 16-byte boundaries
 
     def forward(self, ctx, x, cache, writes_cache: bool = True):
         if not writes_cache:
             raise ConfigError("gated_delta: a recurrent state cannot be shared between layer runs")
         proj = linear(ctx, x, self.w_in)
+        rates = linear(ctx, linear(ctx, x, self.w_low), self.w_rates, out_dtype=torch.float32)
         q, k, v, beta, decay, gate = ops.delta_prep(
-            proj, self.offsets, kv_heads=self.kv_heads, heads=self.heads, dk=self.dk, dv=self.dv, taps=self.taps,
-            rank_a=self.rank_a, rank_g=self.rank_g, conv_w=self.conv_w, a_log=self.a_log, dt_bias=self.dt_bias,
-            a2=self.a2, g2=self.g2, state=cache.state, conv_offset=self.conv_offset, ctx=ctx)
+            proj, rates, self.offsets, kv_heads=self.kv_heads, heads=self.heads, dk=self.dk, dv=self.dv, taps=self.taps,
+            conv_w=self.conv_w, a_log=self.a_log, dt_bias=self.dt_bias, state=cache.state,
+            conv_offset=self.conv_offset, ctx=ctx)
         o = ops.delta_scan(q, k, v, beta, decay, cache.state, ctx, kv_heads=self.kv_heads, heads=self.heads,
                            dk=self.dk, dv=self.dv)
         y = ops.delta_out(o, gate, self.norm, self.eps, heads=self.heads, dv=self.dv, out_dtype=ctx.dtype)
