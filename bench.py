@@ -22,6 +22,12 @@ half of them sharing a 1,024-token prefix, and reports generated tokens a second
 
 `--impl reference` runs the unmodified reference through its own Python primitive API and
 Triton kernels (baseline/reference_arm.py) on the same metric and configuration.
+
+`--design mugizen` measures another architecture of the engine instead of the headline: the
+Mugizen design (parallel blocks of sink attention beside a gated delta rule over a float32
+stream) at layer sizes that resemble a real model's (`--design-sizes s,m,moe`), beside Qwen3 at
+the same width, heads, feed-forward width, layer count and vocabulary: one 2,048-token prefill
+and decode steps at batch 8 and 1 for each, with their shares of the measured peaks.
 """
 from __future__ import annotations
 
@@ -339,6 +345,112 @@ def mixed_run(engine, config, seed=5, requests=32, rate_per_s=16.0):
             "ttft_max_s": ttft[-1], **engine.cache_stats()}
 
 
+# ---------------------------------------------------------------- another design beside Qwen3
+DESIGN_SIZES = {
+    # width, heads, kv heads (head size 128 everywhere), feed-forward, layers, vocabulary, experts
+    "s": dict(width=2048, heads=16, kv=4, ff=8192, layers=4, vocab=32768, moe=None),
+    "m": dict(width=4096, heads=32, kv=8, ff=12288, layers=4, vocab=32768, moe=None),
+    "moe": dict(width=2048, heads=16, kv=4, ff=8192, layers=4, vocab=32768, moe=dict(experts=8, top=2, ff=4096)),
+}
+
+
+def mugizen_config(size):
+    """A Mugizen config.json of these sizes (no layer loop, so that a layer runs once as Qwen3's do)
+    and the tensor shapes that give the sizes the config leaves out."""
+    from vosti_b200.config.mugizen import checkpoint_shapes
+    left = dict(heads=size["heads"], kv_heads=size["kv"], dim=128, vdim=128, scale=128 ** -0.5, bias_max=1024,
+                q_temp=dict(coef=0.1, every=1024))
+    right = dict(heads=size["heads"], kv_heads=size["kv"], dim=128, vdim=128, conv=4)
+    if size["moe"]:
+        mlp = dict(kind="moe", expert=dict(ff=size["moe"]["ff"]), router=dict(experts=size["moe"]["experts"], top=size["moe"]["top"]))
+    else:
+        mlp = dict(kind="dense", ff=size["ff"])
+    config = dict(architecture="Mugizen", vocab=size["vocab"], width=size["width"], norm=dict(eps=1e-6), loop=None,
+                  layers=[dict(type="parallel", mixer=dict(left=left, right=right), mlp=mlp) for _ in range(size["layers"])])
+    return config, checkpoint_shapes(config, bias_rows=32, decay_rank=64, gate_rank=64)
+
+
+def design_flops(size, tokens, design):
+    """Multiply-add work of one prompt of `tokens` tokens, times two: the products and the attention."""
+    W, H, G, F, L, V = size["width"], size["heads"], size["kv"], size["ff"], size["layers"], size["vocab"]
+    d = 128
+    attention = W * (H + 2 * G) * d + H * d * W
+    feed = 3 * W * F if not size["moe"] else 3 * W * size["moe"]["ff"] * size["moe"]["top"]
+    per_token = attention + feed
+    scores = L * H * d * 4.0 * tokens * (tokens + 1) / 2
+    if design == "mugizen":
+        # the recurrent branch: q | k | v | beta, the low-rank pairs (rank 64), the output projection,
+        # and per token and head 4 passes over a 128 x 128 state
+        per_token += W * (2 * G * d + H * d + H) + W * 128 + 128 * 2 * H * d + H * d * W
+        scores += L * tokens * H * 4.0 * d * d
+    return 2.0 * tokens * (L * per_token) + 2.0 * V * W + scores
+
+
+def design_engine(kind, size, max_batch):
+    import torch
+    from vosti_b200 import Engine
+    from vosti_b200.config import model_spec_from_config
+    from vosti_b200.models import expected_weights
+    from vosti_b200.weights import draw_tensors
+
+    if kind == "mugizen":
+        config, shapes = mugizen_config(size)
+        spec = model_spec_from_config(config, shapes)
+    else:
+        spec = model_spec_from_config(qwen3(size["layers"], size["width"], size["heads"], size["kv"], size["ff"],
+                                            context=CONTEXT + 2048) | {"vocab_size": size["vocab"]})
+    tensors = draw_tensors(expected_weights(spec), seed=0, device=torch.device("cuda:0"), dtype=torch.bfloat16)
+    tokens_per_request = CONTEXT + 2 * DECODE_STEPS + 128
+    engine = Engine(spec=spec, tensors=tensors, dtype="bfloat16", device="cuda:0",
+                    num_blocks=max_batch * ((tokens_per_request + PAGE - 1) // PAGE) + 8, block_size=PAGE,
+                    max_num_seqs=max_batch, max_num_batched_tokens=2 * CONTEXT, enable_prefix_caching=False,
+                    cuda_graphs=True, async_scheduling=True, consume_tensors=True)
+    del tensors
+    torch.cuda.empty_cache()
+    return engine
+
+
+def design_main(args) -> int:
+    """Prefill and decode of the Mugizen design beside Qwen3 at equal sizes; one JSON line."""
+    import torch
+
+    peaks, peak_kind = load_peaks()
+    torch.cuda.set_device(0)
+    out = {}
+    for name in args.design_sizes.split(","):
+        size = DESIGN_SIZES[name]
+        row = {}
+        for kind in ("mugizen", "qwen3"):
+            if kind == "qwen3" and size["moe"]:
+                continue                      # the engine has no other model with experts to stand beside
+            engine = design_engine(kind, size, 8)
+            runner = engine.runner
+            weight_bytes = runner.model.weight_bytes()
+            kv_bytes = runner.cache.bytes_per_token()
+            state_bytes = sum(c.state[0].numel() * c.state.element_size() for c in runner.cache.layer_caches
+                              if c.state is not None)
+            prefill_ms = prefill_run(engine, 3, seed=11)
+            tflops = design_flops(size, CONTEXT, kind) / (prefill_ms * 1e-3) / 1e12
+            entry = {"prefill_tok_s": round(CONTEXT * 1e3 / prefill_ms, 1), "prefill_ms": round(prefill_ms, 3),
+                     "prefill_frac_of_bf16_peak": round(tflops / peaks["bf16_tflops"], 4),
+                     "weight_bytes": int(weight_bytes), "kv_bytes_per_token": int(kv_bytes), "state_bytes": int(state_bytes)}
+            for batch in (8, 1):
+                run = decode_run(engine, batch, args.steps, args.warmup, seed=21 + batch, least_repeats=3)
+                step_bytes = weight_bytes + batch * (run["context"] * kv_bytes + 2 * state_bytes)
+                entry[f"decode_b{batch}"] = {
+                    "tok_s": round(batch * 1e3 / run["device_ms"], 1), "ms_per_step": round(run["device_ms"], 4),
+                    "e2e_tok_s": round(batch * 1e3 / run["wall_ms"], 1), "launches": run["launches"],
+                    "frac_of_hbm_peak": round(step_bytes / (run["device_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
+            row[kind] = entry
+            del engine, runner
+            torch.cuda.empty_cache()
+        out[name] = {"sizes": {k: v for k, v in size.items()}, **row}
+    print(json.dumps({"design": "mugizen", "beside": "qwen3 at equal sizes", "context": CONTEXT, "page_size": PAGE,
+                      "steps": args.steps, "warmup": args.warmup, "dtype": "bf16", "peaks": peak_kind,
+                      "data": "synthetic: random token ids, random-init weights", "results": out}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -361,6 +473,9 @@ def main() -> int:
                         help="read every step's tokens before the next step is planned (default: the engine's async scheduling)")
     parser.add_argument("--batch-invariant", default="off", choices=["off", "decode", "full"],
                         help="measure with the engine's bitwise-invariance modes (the default run has them off)")
+    parser.add_argument("--design", default="", choices=["", "mugizen"],
+                        help="measure this design beside Qwen3 at equal layer sizes instead of the headline")
+    parser.add_argument("--design-sizes", default="s,m,moe", help="which of the sizes s, m, moe (comma-separated)")
     args = parser.parse_args()
 
     if args.gpus != 1:
@@ -378,6 +493,10 @@ def main() -> int:
             config["max_position_embeddings"] = max(config["max_position_embeddings"], CONTEXT + 2048)
     if args.impl == "reference":
         return reference_main(args)
+    if args.design:
+        if any(name not in DESIGN_SIZES for name in args.design_sizes.split(",")):
+            parser.error(f"--design-sizes takes {sorted(DESIGN_SIZES)}")
+        return design_main(args)
 
     import torch
     from vosti_b200 import Engine

@@ -326,6 +326,44 @@ def test_expert_mixture_against_plain(dtype, experts, top, ff):
     assert torch.allclose(dense.cpu().sum(-1), torch.ones(T), atol=1e-6) and int((dense != 0).sum()) == T * top
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("experts,top,ff", [(5, 3, 24), (8, 1, 16), (70, 4, 8)])
+def test_expert_mixture_sorted_by_expert_for_long_portions(dtype, experts, top, ff):
+    """A step of prompt portions: pairs sorted by expert, one product per expert with work (some
+    of the 70 experts get none), picks added in pick order. The same result as the stacked way."""
+    gen = torch.Generator().manual_seed(experts + 1)
+    width, T = 72, 300
+    part = build_feed_forward(PartSpec.make("moe", experts=experts, top=top, intermediate_size=ff, float32_out=True), width)
+    W = {k: rounded(*w.shape, gen=gen, std=(3.0 if k == "router" else 1.0) / math.sqrt(w.shape[-1]))
+         for k, w in part.weight_specs().items()}
+    give(part, W, dtype)
+    x = rounded(T, width, gen=gen)
+    ctx = Ctx(dtype)
+    ctx.all_decode = False
+    assert T >= part.GROUPED_FROM
+    before = ops.LAUNCHES
+    got = part.forward(ctx, x.to(DEV, dtype))
+    grouped_launches = ops.LAUNCHES - before
+    want = plain.expert_mixture(x, {"p." + k: v for k, v in W.items()}, "p.", dict(router=dict(top=top)))
+    assert torch.allclose(got.cpu(), want, atol=2e-5 if dtype == torch.float32 else 4e-2)
+    ctx.all_decode = True                       # the stacked way, as a decode step takes it
+    before = ops.LAUNCHES
+    stacked = part.forward(ctx, x.to(DEV, dtype))
+    assert ops.LAUNCHES - before < grouped_launches
+    assert torch.allclose(stacked.cpu(), want, atol=2e-5 if dtype == torch.float32 else 4e-2)
+    logits = (x @ W["router"].T).to(DEV)
+    chosen, _, _ = ops.moe_route(logits, top)
+    offsets, rows, where = ops.moe_group(chosen, experts)
+    offsets, rows, where, chosen = offsets.cpu(), rows.cpu(), where.cpu(), chosen.cpu()
+    assert offsets[0] == 0 and offsets[-1] == T * top and bool((offsets[1:] >= offsets[:-1]).all())
+    for e in range(experts):
+        run = rows[offsets[e]:offsets[e + 1]]
+        assert bool((run[1:] >= run[:-1]).all())                         # inside a run: by pair index
+    assert torch.equal(rows[where.long()], torch.arange(T)[:, None].expand(T, top).int())
+    place_expert = torch.bucketize(where.long(), offsets[1:].long(), right=True)
+    assert torch.equal(place_expert.int(), chosen)
+
+
 # ---------------------------------------------------------------- whole models
 @pytest.fixture(scope="module")
 def models(tmp_path_factory):
@@ -351,7 +389,9 @@ def close_rows(got, want, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["p", "q"])
-def test_whole_prompt_portions_and_decoding_against_plain(models, name, dtype):
+def test_whole_prompt_portions_and_decoding_against_plain(models, name, dtype, monkeypatch):
+    from vosti_b200.parts import ExpertMixture
+    monkeypatch.setattr(ExpertMixture, "GROUPED_FROM", 16)      # portions of 16 tokens or more sort their pairs by expert
     folder, config, W = models[name]
     tokens = prompt(config, 61, 1)
     want = plain.forward(config, W, tokens)

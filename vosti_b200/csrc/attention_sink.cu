@@ -153,15 +153,26 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
 #pragma unroll
     for (int i = 0; i < MAX_W / 32; ++i) acc[i] *= alpha;
     const int last = min(31, kend - j0);
-    for (int kk = 0; kk <= last; ++kk) {
-      const float pk = __shfl_sync(0xffffffffu, p, kk);
-      const int64_t sk = __shfl_sync(0xffffffffu, slot, kk);
-      if (pk == 0.f) continue;
-      const T* vrow = v_cache + sk * dv;
+    // four keys at a time, so that their value rows are in flight together (keys past the
+    // end have p = 0 and slot 0, a row that exists)
+    for (int kk = 0; kk <= last; kk += 4) {
+      float pk[4];
+      const T* vrow[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        pk[u] = __shfl_sync(0xffffffffu, p, kk + u);
+        vrow[u] = v_cache + __shfl_sync(0xffffffffu, slot, kk + u) * dv;
+      }
 #pragma unroll
       for (int i = 0; i < MAX_W / 32; ++i) {
         const int idx = lane + 32 * i;
-        if (idx < dv) acc[i] = fmaf(pk, to_f32(vrow[idx]), acc[i]);
+        if (idx < dv) {
+          float x[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) x[u] = to_f32(vrow[u][idx]);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) acc[i] = fmaf(pk[u], x[u], acc[i]);
+        }
       }
     }
     m = m_new;

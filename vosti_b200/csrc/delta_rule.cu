@@ -28,7 +28,7 @@ namespace {
 constexpr int MAX_TAPS = 16;
 constexpr int SCAN_THREADS = 256;
 constexpr int ROWS = 8;         // key channels a lane keeps
-constexpr int TOKENS = 8;       // tokens staged in shared memory at a time
+constexpr int TOKENS = 16;      // tokens staged in shared memory at a time (in each of two buffers)
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
 __device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
@@ -136,8 +136,19 @@ delta_conv_kernel(const void* proj, int proj_f32, int stride, int off_q, int cc,
 }
 
 // KS lanes of a warp share a value column; lane part `ks` keeps key channels ks * 8 .. ks * 8 + 7
-// of it. A warp holds 32 / KS columns, a block SCAN_THREADS / KS. The staged rows of k, q and g
-// are padded with zeros to KS * 8 channels, so a lane reads its eight as two 16-byte words.
+// of it. A warp holds 32 / KS columns, a block SCAN_THREADS / KS. Tokens are staged in shared
+// memory TOKENS at a time in two buffers: while one block of tokens is computed, the next one's
+// k, q, g, v and beta arrive by cp.async. The staged rows of k, q and g are padded with zeros to
+// KS * 8 channels, so a lane reads its eight as two 16-byte words.
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int KS>
 __global__ void __launch_bounds__(SCAN_THREADS)
 delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
@@ -148,6 +159,7 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
   constexpr int COLS = SCAN_THREADS / KS;       // value columns of a block
   constexpr int PER_WARP = 32 / KS;             // columns of a warp
   constexpr int PAD = KS * ROWS;                // staged channels per token
+  constexpr int STAGE = TOKENS * (3 * PAD + COLS) + TOKENS;      // floats of one buffer (a multiple of 4)
   pdl_wait();
   pdl_launch_dependents();
   const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
@@ -169,30 +181,67 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
 #pragma unroll
     for (int i = 0; i < ROWS; ++i) s[i] = (live && r0 + i < dk) ? S[r0 + i] : 0.f;
   }
-  float* sk = smem;                       // [TOKENS][PAD]
-  float* sq = sk + TOKENS * PAD;
-  float* sg = sq + TOKENS * PAD;
-  float* sv = sg + TOKENS * PAD;          // [TOKENS][COLS]
-  float* sb = sv + TOKENS * COLS;         // [TOKENS]
   const int cq = kv_heads * dk, cd = heads * dk, cv = heads * dv;
-  for (int t0 = 0; t0 < n; t0 += TOKENS) {
+  // 16-byte copies need every row start on a 16-byte boundary
+  const bool vec_k = dk % 4 == 0, vec_v = dv % 4 == 0;
+  if (PAD != dk) {                                  // the padding stays zero (lanes beyond dk multiply it with zeros)
+    for (int i = threadIdx.x; i < 2 * STAGE; i += SCAN_THREADS) smem[i] = 0.f;
+    __syncthreads();
+  }
+
+  auto stage = [&](int t0, int buf) {
+    float* sk = smem + buf * STAGE;
+    float* sq = sk + TOKENS * PAD;
+    float* sg = sq + TOKENS * PAD;
+    float* sv = sg + TOKENS * PAD;
+    float* sb = sv + TOKENS * COLS;
     const int count = min(TOKENS, n - t0);
-    __syncthreads();
-    for (int i = threadIdx.x; i < count * PAD; i += SCAN_THREADS) {
-      const int64_t t = start + t0 + i / PAD;
-      const int c = i % PAD;
-      const bool in = c < dk;
-      sk[i] = in ? k[t * cq + g * dk + c] : 0.f;
-      sq[i] = in ? q[t * cq + g * dk + c] : 0.f;
-      sg[i] = in ? decay[t * cd + h * dk + c] : 0.f;
+    if (vec_k) {
+      const int per = dk / 4;
+      for (int i = threadIdx.x; i < count * per; i += SCAN_THREADS) {
+        const int tt = i / per, c = (i % per) * 4;
+        const int64_t t = start + t0 + tt;
+        cp_async16(sk + tt * PAD + c, k + t * cq + g * dk + c);
+        cp_async16(sq + tt * PAD + c, q + t * cq + g * dk + c);
+        cp_async16(sg + tt * PAD + c, decay + t * cd + h * dk + c);
+      }
+    } else {
+      for (int i = threadIdx.x; i < count * dk; i += SCAN_THREADS) {
+        const int tt = i / dk, c = i % dk;
+        const int64_t t = start + t0 + tt;
+        cp_async4(sk + tt * PAD + c, k + t * cq + g * dk + c);
+        cp_async4(sq + tt * PAD + c, q + t * cq + g * dk + c);
+        cp_async4(sg + tt * PAD + c, decay + t * cd + h * dk + c);
+      }
     }
-    for (int i = threadIdx.x; i < count * COLS; i += SCAN_THREADS) {
-      const int64_t t = start + t0 + i / COLS;
-      const int c = col0 + i % COLS;
-      sv[i] = c < dv ? v[t * cv + h * dv + c] : 0.f;
+    if (vec_v) {
+      const int per = COLS / 4;                   // (COLS is 8 or more)
+      for (int i = threadIdx.x; i < count * per; i += SCAN_THREADS) {
+        const int tt = i / per, c = (i % per) * 4;
+        if (col0 + c < dv) cp_async16(sv + tt * COLS + c, v + (int64_t)(start + t0 + tt) * cv + h * dv + col0 + c);
+      }
+    } else {
+      for (int i = threadIdx.x; i < count * COLS; i += SCAN_THREADS) {
+        const int tt = i / COLS, c = i % COLS;
+        if (col0 + c < dv) cp_async4(sv + tt * COLS + c, v + (int64_t)(start + t0 + tt) * cv + h * dv + col0 + c);
+      }
     }
-    for (int i = threadIdx.x; i < count; i += SCAN_THREADS) sb[i] = beta[(int64_t)(start + t0 + i) * heads + h];
+    for (int i = threadIdx.x; i < count; i += SCAN_THREADS) cp_async4(sb + i, beta + (int64_t)(start + t0 + i) * heads + h);
+  };
+
+  if (n > 0) stage(0, 0);
+  cp_async_commit();
+  for (int t0 = 0, buf = 0; t0 < n; t0 += TOKENS, buf ^= 1) {
+    if (t0 + TOKENS < n) stage(t0 + TOKENS, buf ^ 1);         // (its last readers passed the barrier below)
+    cp_async_commit();
+    cp_async_wait<1>();
     __syncthreads();
+    const float* sk = smem + buf * STAGE;
+    const float* sq = sk + TOKENS * PAD;
+    const float* sg = sq + TOKENS * PAD;
+    const float* sv = sg + TOKENS * PAD;
+    const float* sb = sv + TOKENS * COLS;
+    const int count = min(TOKENS, n - t0);
     for (int tt = 0; tt < count; ++tt) {
       float kt[ROWS], qt[ROWS], gt[ROWS];
       *reinterpret_cast<float4*>(kt) = *reinterpret_cast<const float4*>(sk + tt * PAD + r0);
@@ -226,7 +275,9 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
       for (int o = PER_WARP; o < 32; o <<= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
       if (ks == 0 && live) out[(int64_t)(start + t0 + tt) * cv + h * dv + col] = read;
     }
+    __syncthreads();                                         // this buffer may be refilled two rounds on
   }
+  cp_async_wait<0>();
   if (wide) {
     *reinterpret_cast<float4*>(S + r0) = make_float4(s[0], s[1], s[2], s[3]);
     *reinterpret_cast<float4*>(S + r0 + 4) = make_float4(s[4], s[5], s[6], s[7]);
@@ -304,8 +355,9 @@ VOSTI_API int vosti_delta_scan(const float* q, const float* k, const float* v, c
   const int cols = SCAN_THREADS / ks;
   VOSTI_REQUIRE((dv + cols - 1) / cols <= 65535, "delta_scan: too many value channels");
   const dim3 grid(requests, heads, (dv + cols - 1) / cols);
-  const size_t smem = (size_t)(TOKENS * (3 * ks * ROWS + cols) + TOKENS) * sizeof(float);
+  const size_t smem = 2 * (size_t)(TOKENS * (3 * ks * ROWS + cols) + TOKENS) * sizeof(float);
 #define VOSTI_SCAN(KS)                                                                                              \
+  if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
   vosti_launch(delta_scan_kernel<KS>, grid, dim3(SCAN_THREADS), smem, stream, q, k, v, beta, decay, out, state,    \
                state_stride, cu_q, state_slots, num_slots, kv_heads, heads, dk, dv)
   switch (ks) {

@@ -9,6 +9,12 @@
 // the token's weight for that expert (zero for experts it did not choose), so that one product
 // with the experts' down projections side by side, [width, experts * ff], is the weighted sum
 // of the chosen experts' outputs.
+//
+// For long portions the stacked product would compute every expert for every token. There the
+// (token, pick) pairs are sorted by expert instead (moe_group: one block counts, scans and
+// places them, so the order inside an expert's run is by pair index and the same every time),
+// every expert multiplies its own run of gathered rows, and moe_combine adds a token's picks in
+// the order of its picks: out[t] = sum_k w[t, k] * y[where[t, k]].
 #include "common.cuh"
 
 namespace {
@@ -69,7 +75,78 @@ __global__ void moe_scale_kernel(T* __restrict__ act, const float* __restrict__ 
   }
 }
 
+// One block. chosen: [pairs] expert of every (token, pick) pair, pair = token * top + pick.
+// offsets [experts + 1]: where each expert's run starts in the sorted order; rows [pairs]: the
+// token of the pair at each sorted place; where [pairs]: the sorted place of each pair.
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int* __restrict__ chosen, int pairs, int top, int experts, int* __restrict__ offsets,
+                 int* __restrict__ rows, int* __restrict__ where) {
+  extern __shared__ int counts[];           // [experts + 1]
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int e = threadIdx.x; e <= experts; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = chosen[i];
+    if (e >= 0 && e < experts) atomicAdd(&counts[e + 1], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int e = 0; e < experts; ++e) counts[e + 1] += counts[e];
+    for (int e = 0; e <= experts; ++e) offsets[e] = counts[e];
+  }
+  __syncthreads();
+  // a pair's place: its expert's start plus the number of earlier pairs of the same expert.
+  // One warp per expert walks the pairs in order, so the placement never varies.
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int e = warp; e < experts; e += nwarps) {
+    int at = counts[e];
+    for (int i0 = 0; i0 < pairs; i0 += 32) {
+      const int i = i0 + lane;
+      const bool mine = i < pairs && chosen[i] == e;
+      const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+      if (mine) {
+        const int place = at + __popc(ballot & ((1u << lane) - 1u));
+        rows[place] = i / top;
+        where[i] = place;
+      }
+      at += __popc(ballot);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ where, const float* __restrict__ weights,
+                   float* __restrict__ out, int top, int width) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k)
+      acc = fmaf(weights[(int64_t)t * top + k], y[(int64_t)where[(int64_t)t * top + k] * width + c], acc);
+    out[(int64_t)t * width + c] = acc;
+  }
+}
+
 }  // namespace
+
+VOSTI_API int vosti_moe_group(const int* chosen, int tokens, int top, int experts, int* offsets, int* rows, int* where,
+                              cudaStream_t stream) {
+  VOSTI_REQUIRE(tokens >= 0 && top > 0 && experts > 0 && experts <= 8192, "moe_group: bad sizes");
+  VOSTI_REQUIRE((int64_t)tokens * top < (int64_t)1 << 30, "moe_group: too many pairs");
+  vosti_launch(moe_group_kernel, dim3(1), dim3(1024), (size_t)(experts + 1) * sizeof(int), stream, chosen, tokens * top, top,
+               experts, offsets, rows, where);
+  VOSTI_LAUNCH_CHECK();
+}
+
+VOSTI_API int vosti_moe_combine(const float* y, const int* where, const float* weights, float* out, int tokens, int top,
+                                int width, cudaStream_t stream) {
+  VOSTI_REQUIRE(tokens >= 0 && top > 0 && width > 0, "moe_combine: bad sizes");
+  if (tokens == 0) return VOSTI_OK;
+  vosti_launch(moe_combine_kernel, dim3(tokens), dim3(256), 0, stream, y, where, weights, out, top, width);
+  VOSTI_LAUNCH_CHECK();
+}
 
 VOSTI_API int vosti_moe_route(const float* logits, int tokens, int experts, int top, int* chosen, float* weights,
                               float* dense, cudaStream_t stream) {

@@ -772,28 +772,24 @@ def attention_sink(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     table float32 [nq, distances] (base-2 units, the last column serving every larger distance)
     and an optional sink logit per head (float32 [nq], natural units). Returns [tokens, nq * dv].
     bfloat16 with equal key and value widths of 64 or 128 (pages of a multiple of 16 tokens, at
-    most 16 query heads per kv head): the step's long rows run on the tensor-memory kernel,
-    its short ones (the step's work lists: attention_step_layout) on the CUDA cores with the keys
-    cut into segments. Everything else runs on the CUDA-core kernel."""
+    most 16 query heads per kv head): every row of the step, long or a single token, runs on the
+    tensor-memory kernel, whose rows are independent of one another. Everything else runs on the
+    CUDA-core kernel, with the keys cut into segments when the step has few rows."""
     _contig(q, k_cache, v_cache, bias, sink)
     tokens = q.shape[0]
     out = torch.empty((tokens, nq * dv), dtype=q.dtype, device=q.device)
     common = dict(nq=nq, nkv=nkv, dk=dk, dv=dv, scale=scale, window=window, bias=bias, sink=sink)
     lib = library()
-    lists = ctx.layout.get("attention") if getattr(ctx, "layout", None) else None
-    tensor_memory = (q.dtype == torch.bfloat16 and dk == dv and nq // nkv <= 16 and lists is not None
-                     and lists["num_long_rows"] > 0 and lib.vosti_attention_prefill_tc_supported(dk, group.page_size))
+    tensor_memory = (q.dtype == torch.bfloat16 and dk == dv and nq // nkv <= 16
+                     and lib.vosti_attention_prefill_tc_supported(dk, group.page_size))
     if not tensor_memory:
         _attention_sink_rows(ctx, q, k_cache, v_cache, out, group, token_list=None, count=tokens, **common)
         return out
-    if lists["num_short_tokens"]:
-        _attention_sink_rows(ctx, q, k_cache, v_cache, out, group, token_list=ctx.extras.get("attention.short_tokens"),
-                             count=lists["num_short_tokens"], **common)
     num_pages = k_cache.numel() // (group.page_size * nkv * dk)
     _check(lib.vosti_attention_prefill_tc_biased(
-        _p(q), _p(k_cache), _p(v_cache), _p(out), _p(ctx.extras.get("attention.long_rows")), lists["num_long_rows"],
+        _p(q), _p(k_cache), _p(v_cache), _p(out), None, ctx.num_requests,
         _p(ctx.cu_q), _p(ctx.kv_len), _p(group.block_table), group.block_table.shape[1], group.page_size, num_pages, nq,
-        nkv, dk, lists["max_long_q_len"], tokens, ctypes.c_float(scale), window, _p(bias),
+        nkv, dk, ctx.max_q_len, tokens, ctypes.c_float(scale), window, _p(bias),
         0 if bias is None else bias.shape[1] - 1, _p(sink), _p(ctx.status), _stream()), "attention_prefill_tc_biased")
     return out
 
@@ -869,3 +865,29 @@ def moe_scale(act: torch.Tensor, dense: torch.Tensor, ff: int) -> torch.Tensor:
     _check(library().vosti_moe_scale(_p(act), _p(dense), act.shape[0], dense.shape[1], ff, _is_f32(act), _stream()),
            "moe_scale")
     return act
+
+
+def moe_group(chosen: torch.Tensor, experts: int):
+    """Sort the (token, pick) pairs of `chosen` int32 [tokens, top] by expert, keeping their order
+    inside an expert: (offsets int32 [experts + 1] of every expert's run, rows int32 [pairs] the
+    token at each sorted place, where int32 [tokens, top] the sorted place of every pair)."""
+    _contig(chosen)
+    tokens, top = chosen.shape
+    offsets = torch.empty((experts + 1,), dtype=torch.int32, device=chosen.device)
+    rows = torch.empty((tokens * top,), dtype=torch.int32, device=chosen.device)
+    where = torch.empty((tokens, top), dtype=torch.int32, device=chosen.device)
+    _check(library().vosti_moe_group(_p(chosen), tokens, top, experts, _p(offsets), _p(rows), _p(where), _stream()),
+           "moe_group")
+    return offsets, rows, where
+
+
+def moe_combine(y: torch.Tensor, where: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_k weights[t, k] * y[where[t, k]], float32."""
+    _contig(y, where, weights)
+    if y.dtype != torch.float32 or weights.dtype != torch.float32:
+        raise KernelError("moe_combine: the experts' outputs and the weights are float32")
+    tokens, top = where.shape
+    out = torch.empty((tokens, y.shape[1]), dtype=torch.float32, device=y.device)
+    _check(library().vosti_moe_combine(_p(y), _p(where), _p(weights), _p(out), tokens, top, y.shape[1], _stream()),
+           "moe_combine")
+    return out

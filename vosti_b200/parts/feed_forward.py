@@ -90,7 +90,16 @@ class ExpertMixture(FeedForward):
     token's activation is computed for all experts by one product, each expert's slice is
     multiplied by the token's weight for it (zero if it was not chosen), and one more product
     sums the chosen experts' outputs. No launch depends on the router's choice, so a step may be
-    replayed from a CUDA graph."""
+    replayed from a CUDA graph.
+
+    A step that brings portions of prompts (`GROUPED_FROM` tokens or more, not all of them single
+    tokens; such a step is never recorded as a graph) takes another way, in which no expert
+    computes a token that did not choose it: the (token, pick) pairs are sorted by expert on the
+    device, the host reads how many each expert got (one synchronisation), every expert with
+    work multiplies its run of gathered rows, and a last kernel adds every token's picks in pick
+    order. The experts' gate and up matrices are kept a second time for it, one per expert."""
+
+    GROUPED_FROM = 256
 
     def __init__(self, spec: PartSpec, hidden_size: int):
         super().__init__(spec, hidden_size)
@@ -115,14 +124,35 @@ class ExpertMixture(FeedForward):
         up = torch.cat([tensors[f"e{e}.up"] for e in range(self.experts)], dim=0)
         self.w_gate_up, self.fused = stack_gate_up(gate, up, dtype)
         self.w_down = prepare_weight(torch.cat([tensors[f"e{e}.down"] for e in range(self.experts)], dim=1).contiguous(), dtype)
+        self.per_expert = []
+        if self.top < self.experts:
+            for e in range(self.experts):
+                gate_up, fused = stack_gate_up(tensors[f"e{e}.gate"], tensors[f"e{e}.up"], dtype)
+                self.per_expert.append((gate_up, fused, prepare_weight(tensors[f"e{e}.down"], dtype)))
 
     def first_weight(self):
         return self.w_gate_up
 
+    def _grouped(self, ctx, x, chosen, weights):
+        offsets, rows, where = ops.moe_group(chosen, self.experts)
+        gathered = ops.gather_rows(x, rows, ctx.status)
+        bounds = offsets.tolist()                      # the host learns the experts' shares here
+        y = torch.empty((rows.shape[0], self.hidden_size), dtype=torch.float32, device=x.device)
+        for e, (gate_up, fused, down) in enumerate(self.per_expert):
+            lo, hi = bounds[e], bounds[e + 1]
+            if hi > lo:
+                act = gated_activation(ctx, gathered[lo:hi], gate_up, fused)
+                y[lo:hi].copy_(linear(ctx, act, down, out_dtype=torch.float32))
+        return ops.moe_combine(y, where, weights)
+
     def forward(self, ctx, x):
         x = ops.materialize(x)
         logits = ops.gemm_simt(x, self.router, ctx.status, out_dtype=torch.float32)
-        _, _, dense = ops.moe_route(logits, self.top)
+        chosen, weights, dense = ops.moe_route(logits, self.top)
+        if (self.per_expert and x.shape[0] >= self.GROUPED_FROM and not getattr(ctx, "all_decode", True)
+                and not torch.cuda.is_current_stream_capturing()):
+            out = self._grouped(ctx, x, chosen, weights)
+            return out if self.float32_out else out.to(x.dtype)
         act = ops.moe_scale(gated_activation(ctx, x, self.w_gate_up, self.fused), dense, self.inter)
         if self.float32_out:
             return linear(ctx, act, self.w_down, out_dtype=torch.float32)
