@@ -71,7 +71,26 @@ qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict
   const T* row = qkv + (int64_t)t * (wq + wk + wv);
   float temp = 1.f;
   if (temp_coef != 0.f) temp = 1.f + temp_coef * logf((float)((positions[t] + 1) / temp_every + 1));
-  for (int i = threadIdx.x; i < wq; i += blockDim.x) q_out[(int64_t)t * wq + i] = from_f32<T>(to_f32(row[i]) * temp);
+  // bfloat16 rows whose widths allow it move as 16-byte words (8 elements)
+  const bool vec = sizeof(T) == 2 && dk % 8 == 0 && dv % 8 == 0;
+  if (vec) {
+    const uint4* src = reinterpret_cast<const uint4*>(row);
+    uint4* dst = reinterpret_cast<uint4*>(q_out + (int64_t)t * wq);
+    for (int i = threadIdx.x; i < wq / 8; i += blockDim.x) {
+      uint4 raw = src[i];
+      if (temp != 1.f) {
+        __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(p[j]);
+          p[j] = __floats2bfloat162_rn(f.x * temp, f.y * temp);
+        }
+      }
+      dst[i] = raw;
+    }
+  } else {
+    for (int i = threadIdx.x; i < wq; i += blockDim.x) q_out[(int64_t)t * wq + i] = from_f32<T>(to_f32(row[i]) * temp);
+  }
   if (k_cache == nullptr) return;
   const int64_t slot = slot_mapping[t];
   if (slot < 0 || slot >= num_slots) {
@@ -79,6 +98,19 @@ qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict
     return;
   }
   const int64_t page = slot / page_size, offset = slot % page_size;
+  if (vec) {
+    const uint4* src = reinterpret_cast<const uint4*>(row);
+    const int k8 = dk / 8, v8 = dv / 8;
+    for (int i = threadIdx.x; i < wk / 8; i += blockDim.x) {
+      const int g = i / k8, c = i % k8;
+      reinterpret_cast<uint4*>(k_cache + ((page * nkv + g) * page_size + offset) * dk)[c] = src[wq / 8 + i];
+    }
+    for (int i = threadIdx.x; i < wv / 8; i += blockDim.x) {
+      const int g = i / v8, c = i % v8;
+      reinterpret_cast<uint4*>(v_cache + ((page * nkv + g) * page_size + offset) * dv)[c] = src[(wq + wk) / 8 + i];
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < wk; i += blockDim.x) {
     const int g = i / dk, c = i % dk;
     k_cache[((page * nkv + g) * page_size + offset) * dk + c] = row[wq + i];

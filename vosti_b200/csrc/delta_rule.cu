@@ -19,15 +19,16 @@
 //   delta_scan     one block per (request, head, block of value columns): the recurrence over
 //                  the request's tokens of this step, from and to the state slot. Columns of S
 //                  are independent; a column's dk entries are spread over KS lanes of a warp,
-//                  8 contiguous ones to a lane, and the two sums over them are shuffles.
+//                  R contiguous ones to a lane, and the two sums over them are shuffles.
 //   delta_out      one warp per (token, head): the output stage
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace {
 
 constexpr int MAX_TAPS = 16;
-constexpr int SCAN_THREADS = 256;
-constexpr int ROWS = 8;         // key channels a lane keeps
+constexpr int SCAN_THREADS = 256; // most threads of a scan block
 constexpr int TOKENS = 16;      // tokens staged in shared memory at a time (in each of two buffers)
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
@@ -135,11 +136,13 @@ delta_conv_kernel(const void* proj, int proj_f32, int stride, int off_q, int cc,
   }
 }
 
-// KS lanes of a warp share a value column; lane part `ks` keeps key channels ks * 8 .. ks * 8 + 7
-// of it. A warp holds 32 / KS columns, a block SCAN_THREADS / KS. Tokens are staged in shared
-// memory TOKENS at a time in two buffers: while one block of tokens is computed, the next one's
-// k, q, g, v and beta arrive by cp.async. The staged rows of k, q and g are padded with zeros to
-// KS * 8 channels, so a lane reads its eight as two 16-byte words.
+// KS lanes of a warp share a value column; lane part `ks` keeps key channels ks * R .. ks * R + R - 1
+// of it. A warp holds 32 / KS columns, a block (its thread count) / KS. Tokens are staged in
+// shared memory TOKENS at a time in two buffers: while one block of tokens is computed, the next
+// one's k, q, g, v and beta arrive by cp.async. The staged rows of k, q and g are padded with
+// zeros to KS * R channels, so a lane reads its R as 16-byte words. Between two tokens the state
+// waits for one chain of multiply-adds and one chain of KS-lane shuffles; both wait on the
+// shared-memory and shuffle pipe, so R is chosen for few shuffle steps (see the launcher).
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
@@ -149,17 +152,18 @@ __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int KS>
+template <int KS, int R>
 __global__ void __launch_bounds__(SCAN_THREADS)
 delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ out,
                   float* state, int64_t state_stride, const int* __restrict__ cu_q, const int* __restrict__ state_slots,
                   int num_slots, int kv_heads, int heads, int dk, int dv) {
   extern __shared__ __align__(16) float smem[];
-  constexpr int COLS = SCAN_THREADS / KS;       // value columns of a block
   constexpr int PER_WARP = 32 / KS;             // columns of a warp
-  constexpr int PAD = KS * ROWS;                // staged channels per token
-  constexpr int STAGE = TOKENS * (3 * PAD + COLS) + TOKENS;      // floats of one buffer (a multiple of 4)
+  constexpr int PAD = KS * R;                   // staged channels per token
+  const int threads = blockDim.x;
+  const int COLS = threads / KS;                // value columns of a block (8 or more)
+  const int STAGE = TOKENS * (3 * PAD + COLS) + TOKENS;      // floats of one buffer (a multiple of 4)
   pdl_wait();
   pdl_launch_dependents();
   const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
@@ -170,22 +174,22 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int ks = lane / PER_WARP, local = warp * PER_WARP + lane % PER_WARP, col = col0 + local;
   const bool live = col < dv;
-  const int r0 = ks * ROWS;
+  const int r0 = ks * R;
   float* S = state + (int64_t)slot * state_stride + ((int64_t)h * dv + col) * dk;     // this column's dk channels
-  float s[ROWS];
-  const bool wide = (dk % 4 == 0) && live && r0 + ROWS <= dk;
+  float s[R];
+  const bool wide = (dk % 4 == 0) && live && r0 + R <= dk;
   if (wide) {
-    const float4 lo = *reinterpret_cast<const float4*>(S + r0), hi = *reinterpret_cast<const float4*>(S + r0 + 4);
-    s[0] = lo.x; s[1] = lo.y; s[2] = lo.z; s[3] = lo.w; s[4] = hi.x; s[5] = hi.y; s[6] = hi.z; s[7] = hi.w;
+#pragma unroll
+    for (int i = 0; i < R; i += 4) *reinterpret_cast<float4*>(s + i) = *reinterpret_cast<const float4*>(S + r0 + i);
   } else {
 #pragma unroll
-    for (int i = 0; i < ROWS; ++i) s[i] = (live && r0 + i < dk) ? S[r0 + i] : 0.f;
+    for (int i = 0; i < R; ++i) s[i] = (live && r0 + i < dk) ? S[r0 + i] : 0.f;
   }
   const int cq = kv_heads * dk, cd = heads * dk, cv = heads * dv;
   // 16-byte copies need every row start on a 16-byte boundary
   const bool vec_k = dk % 4 == 0, vec_v = dv % 4 == 0;
   if (PAD != dk) {                                  // the padding stays zero (lanes beyond dk multiply it with zeros)
-    for (int i = threadIdx.x; i < 2 * STAGE; i += SCAN_THREADS) smem[i] = 0.f;
+    for (int i = threadIdx.x; i < 2 * STAGE; i += threads) smem[i] = 0.f;
     __syncthreads();
   }
 
@@ -198,7 +202,7 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     const int count = min(TOKENS, n - t0);
     if (vec_k) {
       const int per = dk / 4;
-      for (int i = threadIdx.x; i < count * per; i += SCAN_THREADS) {
+      for (int i = threadIdx.x; i < count * per; i += threads) {
         const int tt = i / per, c = (i % per) * 4;
         const int64_t t = start + t0 + tt;
         cp_async16(sk + tt * PAD + c, k + t * cq + g * dk + c);
@@ -206,7 +210,7 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         cp_async16(sg + tt * PAD + c, decay + t * cd + h * dk + c);
       }
     } else {
-      for (int i = threadIdx.x; i < count * dk; i += SCAN_THREADS) {
+      for (int i = threadIdx.x; i < count * dk; i += threads) {
         const int tt = i / dk, c = i % dk;
         const int64_t t = start + t0 + tt;
         cp_async4(sk + tt * PAD + c, k + t * cq + g * dk + c);
@@ -215,20 +219,21 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
       }
     }
     if (vec_v) {
-      const int per = COLS / 4;                   // (COLS is 8 or more)
-      for (int i = threadIdx.x; i < count * per; i += SCAN_THREADS) {
+      const int per = COLS / 4;
+      for (int i = threadIdx.x; i < count * per; i += threads) {
         const int tt = i / per, c = (i % per) * 4;
         if (col0 + c < dv) cp_async16(sv + tt * COLS + c, v + (int64_t)(start + t0 + tt) * cv + h * dv + col0 + c);
       }
     } else {
-      for (int i = threadIdx.x; i < count * COLS; i += SCAN_THREADS) {
+      for (int i = threadIdx.x; i < count * COLS; i += threads) {
         const int tt = i / COLS, c = i % COLS;
         if (col0 + c < dv) cp_async4(sv + tt * COLS + c, v + (int64_t)(start + t0 + tt) * cv + h * dv + col0 + c);
       }
     }
-    for (int i = threadIdx.x; i < count; i += SCAN_THREADS) cp_async4(sb + i, beta + (int64_t)(start + t0 + i) * heads + h);
+    for (int i = threadIdx.x; i < count; i += threads) cp_async4(sb + i, beta + (int64_t)(start + t0 + i) * heads + h);
   };
 
+  float* orow = out + (int64_t)start * cv + h * dv + col;
   if (n > 0) stage(0, 0);
   cp_async_commit();
   for (int t0 = 0, buf = 0; t0 < n; t0 += TOKENS, buf ^= 1) {
@@ -236,54 +241,51 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    const float* sk = smem + buf * STAGE;
+    const float* sk = smem + buf * STAGE + r0;
     const float* sq = sk + TOKENS * PAD;
     const float* sg = sq + TOKENS * PAD;
-    const float* sv = sg + TOKENS * PAD;
-    const float* sb = sv + TOKENS * COLS;
+    const float* sv = smem + buf * STAGE + 3 * TOKENS * PAD + local;
+    const float* sb = smem + buf * STAGE + 3 * TOKENS * PAD + TOKENS * COLS;
     const int count = min(TOKENS, n - t0);
     for (int tt = 0; tt < count; ++tt) {
-      float kt[ROWS], qt[ROWS], gt[ROWS];
-      *reinterpret_cast<float4*>(kt) = *reinterpret_cast<const float4*>(sk + tt * PAD + r0);
-      *reinterpret_cast<float4*>(kt + 4) = *reinterpret_cast<const float4*>(sk + tt * PAD + r0 + 4);
-      *reinterpret_cast<float4*>(gt) = *reinterpret_cast<const float4*>(sg + tt * PAD + r0);
-      *reinterpret_cast<float4*>(gt + 4) = *reinterpret_cast<const float4*>(sg + tt * PAD + r0 + 4);
-      *reinterpret_cast<float4*>(qt) = *reinterpret_cast<const float4*>(sq + tt * PAD + r0);
-      *reinterpret_cast<float4*>(qt + 4) = *reinterpret_cast<const float4*>(sq + tt * PAD + r0 + 4);
-      float d0 = 0.f, d1 = 0.f;
+      float kt[R], x[R];
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < ROWS; i += 2) {
-        s[i] *= gt[i];
-        s[i + 1] *= gt[i + 1];
-        d0 = fmaf(s[i], kt[i], d0);
-        d1 = fmaf(s[i + 1], kt[i + 1], d1);
+      for (int i = 0; i < R; i += 4) {
+        *reinterpret_cast<float4*>(kt + i) = *reinterpret_cast<const float4*>(sk + tt * PAD + i);
+        *reinterpret_cast<float4*>(x + i) = *reinterpret_cast<const float4*>(sg + tt * PAD + i);
       }
-      float dot = d0 + d1;
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        s[i] *= x[i];
+        acc[i & 3] = fmaf(s[i], kt[i], acc[i & 3]);
+      }
+      float dot = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+      for (int i = 0; i < R; i += 4) *reinterpret_cast<float4*>(x + i) = *reinterpret_cast<const float4*>(sq + tt * PAD + i);
 #pragma unroll
       for (int o = PER_WARP; o < 32; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float u = sb[tt] * (sv[tt * COLS + local] - dot);
-      float e0 = 0.f, e1 = 0.f;
+      const float u = sb[tt] * (sv[tt * COLS] - dot);
+      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
 #pragma unroll
-      for (int i = 0; i < ROWS; i += 2) {
+      for (int i = 0; i < R; ++i) {
         s[i] = fmaf(kt[i], u, s[i]);
-        s[i + 1] = fmaf(kt[i + 1], u, s[i + 1]);
-        e0 = fmaf(s[i], qt[i], e0);
-        e1 = fmaf(s[i + 1], qt[i + 1], e1);
+        acc[i & 3] = fmaf(s[i], x[i], acc[i & 3]);
       }
-      float read = e0 + e1;
+      float read = (acc[0] + acc[1]) + (acc[2] + acc[3]);
 #pragma unroll
       for (int o = PER_WARP; o < 32; o <<= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
-      if (ks == 0 && live) out[(int64_t)(start + t0 + tt) * cv + h * dv + col] = read;
+      if (ks == 0 && live) orow[(int64_t)(t0 + tt) * cv] = read;
     }
     __syncthreads();                                         // this buffer may be refilled two rounds on
   }
   cp_async_wait<0>();
   if (wide) {
-    *reinterpret_cast<float4*>(S + r0) = make_float4(s[0], s[1], s[2], s[3]);
-    *reinterpret_cast<float4*>(S + r0 + 4) = make_float4(s[4], s[5], s[6], s[7]);
+#pragma unroll
+    for (int i = 0; i < R; i += 4) *reinterpret_cast<float4*>(S + r0 + i) = *reinterpret_cast<const float4*>(s + i);
   } else {
 #pragma unroll
-    for (int i = 0; i < ROWS; ++i)
+    for (int i = 0; i < R; ++i)
       if (live && r0 + i < dk) S[r0 + i] = s[i];
   }
 }
@@ -342,32 +344,55 @@ VOSTI_API int vosti_delta_prep(const void* proj, int proj_f32, int stride, int o
   VOSTI_LAUNCH_CHECK();
 }
 
+// How many key channels a lane keeps (8, 16 or 32). VOSTI_SCAN_ROWS overrides the rule (tuning).
+static int scan_rows(int dk) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char* env = getenv("VOSTI_SCAN_ROWS");
+    forced = env != nullptr ? atoi(env) : 0;
+  }
+  if ((forced == 8 || forced == 16 || forced == 32) && dk <= forced * 32 && (forced != 32 || dk <= 256)) return forced;
+  return dk <= 32 ? 8 : 16;
+}
+
 VOSTI_API int vosti_delta_scan(const float* q, const float* k, const float* v, const float* beta, const float* decay,
                                float* out, float* state, int64_t state_stride, const int* cu_q, const int* state_slots,
                                int num_slots, int requests, int kv_heads, int heads, int dk, int dv, cudaStream_t stream) {
   VOSTI_REQUIRE(kv_heads > 0 && heads > 0 && heads % kv_heads == 0 && dk > 0 && dv > 0, "delta_scan: bad head sizes");
-  VOSTI_REQUIRE(dk <= ROWS * 32, "delta_scan: %d key channels (at most %d are taken)", dk, ROWS * 32);
+  VOSTI_REQUIRE(dk <= 256, "delta_scan: %d key channels (at most 256 are taken)", dk);
   VOSTI_REQUIRE(heads <= 65535, "delta_scan: too many heads");
   VOSTI_REQUIRE(state_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(state) & 15) == 0, "delta_scan: state slots must be 16-byte aligned");
   if (requests == 0) return VOSTI_OK;
+  const int rows = scan_rows(dk);
   int ks = 1;
-  while (ks * ROWS < dk) ks *= 2;
-  const int cols = SCAN_THREADS / ks;
+  while (ks * rows < dk) ks *= 2;
+  // blocks of 8 columns or more; smaller blocks while the grid would leave SMs idle
+  int threads = SCAN_THREADS;
+  while (threads > 64 && threads / 2 >= 8 * ks &&
+         (int64_t)requests * heads * ((dv + threads / ks - 1) / (threads / ks)) < 296)
+    threads /= 2;
+  if (threads < 8 * ks) threads = 8 * ks;
+  const int cols = threads / ks;
   VOSTI_REQUIRE((dv + cols - 1) / cols <= 65535, "delta_scan: too many value channels");
   const dim3 grid(requests, heads, (dv + cols - 1) / cols);
-  const size_t smem = 2 * (size_t)(TOKENS * (3 * ks * ROWS + cols) + TOKENS) * sizeof(float);
-#define VOSTI_SCAN(KS)                                                                                              \
-  if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-  vosti_launch(delta_scan_kernel<KS>, grid, dim3(SCAN_THREADS), smem, stream, q, k, v, beta, decay, out, state,    \
-               state_stride, cu_q, state_slots, num_slots, kv_heads, heads, dk, dv)
-  switch (ks) {
-    case 1: VOSTI_SCAN(1); break;
-    case 2: VOSTI_SCAN(2); break;
-    case 4: VOSTI_SCAN(4); break;
-    case 8: VOSTI_SCAN(8); break;
-    case 16: VOSTI_SCAN(16); break;
-    default: VOSTI_SCAN(32); break;
+  const size_t smem = 2 * (size_t)(TOKENS * (3 * ks * rows + cols) + TOKENS) * sizeof(float);
+#define VOSTI_SCAN(KS, R)                                                                                           \
+  do {                                                                                                              \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<KS, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    vosti_launch(delta_scan_kernel<KS, R>, grid, dim3(threads), smem, stream, q, k, v, beta, decay, out, state,    \
+                 state_stride, cu_q, state_slots, num_slots, kv_heads, heads, dk, dv);                              \
+  } while (0)
+#define VOSTI_SCAN_KS(R)                                                                                            \
+  switch (ks) {                                                                                                     \
+    case 1: VOSTI_SCAN(1, R); break;                                                                                \
+    case 2: VOSTI_SCAN(2, R); break;                                                                                \
+    case 4: VOSTI_SCAN(4, R); break;                                                                                \
+    case 8: VOSTI_SCAN(8, R); break;                                                                                \
+    case 16: VOSTI_SCAN(16, R); break;                                                                              \
+    default: VOSTI_SCAN(32, R); break;                                                                              \
   }
+  if (rows == 8) { VOSTI_SCAN_KS(8) } else if (rows == 16) { VOSTI_SCAN_KS(16) } else { VOSTI_SCAN_KS(32) }
+#undef VOSTI_SCAN_KS
 #undef VOSTI_SCAN
   VOSTI_LAUNCH_CHECK();
 }

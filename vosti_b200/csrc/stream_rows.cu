@@ -14,6 +14,24 @@ __device__ __forceinline__ float term_at(const void* p, int is_f32, int64_t i) {
   return p == nullptr ? 0.f : load_flex(p, is_f32, i);
 }
 
+// Four neighbouring elements starting at i (a multiple of 4) of an array whose type is chosen at
+// run time: one 16-byte word of floats or one 8-byte word of bfloat16.
+__device__ __forceinline__ float4 load_flex4(const void* p, int is_f32, int64_t i) {
+  if (is_f32) return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+  const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(p) + i);
+  const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const unsigned*>(&lo);
+  raw.y = *reinterpret_cast<const unsigned*>(&hi);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
 // x = stream + t1 + t2 (any of them absent); stream_out <- x; out <- tanh(alpha x) * w + b.
 template <typename TO>
 __global__ void __launch_bounds__(256)
@@ -23,6 +41,19 @@ dyt_kernel(const float* stream, const void* t1, int t1_f32, const void* t2, int 
   pdl_wait();
   pdl_launch_dependents();
   const int64_t base = (int64_t)blockIdx.x * width;
+  if (width % 4 == 0) {          // the same arithmetic, four elements to a thread
+    for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+      float4 x = stream != nullptr ? *reinterpret_cast<const float4*>(stream + base + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      if (t1 != nullptr) { const float4 a = load_flex4(t1, t1_f32, base + i); x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w; }
+      if (t2 != nullptr) { const float4 a = load_flex4(t2, t2_f32, base + i); x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w; }
+      if (stream_out != nullptr) *reinterpret_cast<float4*>(stream_out + base + i) = x;
+      const float4 w = load_flex4(weight, wb_f32, i);
+      float4 y = make_float4(tanhf(alpha * x.x) * w.x, tanhf(alpha * x.y) * w.y, tanhf(alpha * x.z) * w.z, tanhf(alpha * x.w) * w.w);
+      if (bias != nullptr) { const float4 b = load_flex4(bias, wb_f32, i); y.x += b.x; y.y += b.y; y.z += b.z; y.w += b.w; }
+      store4(out + base + i, y);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float x = stream != nullptr ? stream[base + i] : 0.f;
     if (t1 != nullptr) x += load_flex(t1, t1_f32, base + i);
@@ -71,17 +102,37 @@ branch_merge_kernel(Branches br, int w_f32, float* __restrict__ out, int width, 
   pdl_wait();
   pdl_launch_dependents();
   const int64_t base = (int64_t)blockIdx.x * width;
+  const bool vec = width % 4 == 0;
   for (int b = 0; b < br.count; ++b) {
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-      const float v = load_flex(br.x[b], br.x_f32[b], base + i);
-      ss += v * v;
+    if (vec) {
+      for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+        const float4 v = load_flex4(br.x[b], br.x_f32[b], base + i);
+        ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+      }
+    } else {
+      for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = load_flex(br.x[b], br.x_f32[b], base + i);
+        ss += v * v;
+      }
     }
     const float total = block_sum(ss, scratch);
     if (threadIdx.x == 0) inv_rms[b] = 1.f / sqrtf(total / (float)width + eps);
   }
   __syncthreads();
   const float share = 1.f / (float)br.count;
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int b = 0; b < br.count; ++b) {
+        const float4 v = load_flex4(br.x[b], br.x_f32[b], base + i), w = load_flex4(br.w[b], w_f32, i);
+        const float r = inv_rms[b];
+        acc.x += v.x * r * w.x; acc.y += v.y * r * w.y; acc.z += v.z * r * w.z; acc.w += v.w * r * w.w;
+      }
+      *reinterpret_cast<float4*>(out + base + i) = make_float4(acc.x * share, acc.y * share, acc.z * share, acc.w * share);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float acc = 0.f;
     for (int b = 0; b < br.count; ++b)

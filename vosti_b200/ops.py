@@ -745,7 +745,8 @@ def qkv_store(qkv: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optio
     return q
 
 
-SINK_SEGMENT = 256          # keys per segment when few query rows share the GPU
+SINK_DECODE_ON_CORES = _os.environ.get("VOSTI_SINK_DECODE_ON_CORES", "0") == "1"   # decode steps off the tensor-memory kernel
+SINK_SEGMENT = int(_os.environ.get("VOSTI_SINK_SEGMENT", "256"))          # keys per segment when few query rows share the GPU
 SINK_SPLIT_MAX_ROWS = 2048  # (token, head) rows up to which the keys are cut into segments
 
 
@@ -782,7 +783,7 @@ def attention_sink(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     lib = library()
     tensor_memory = (q.dtype == torch.bfloat16 and dk == dv and nq // nkv <= 16
                      and lib.vosti_attention_prefill_tc_supported(dk, group.page_size))
-    if not tensor_memory:
+    if not tensor_memory or (SINK_DECODE_ON_CORES and ctx.all_decode):
         _attention_sink_rows(ctx, q, k_cache, v_cache, out, group, token_list=None, count=tokens, **common)
         return out
     num_pages = k_cache.numel() // (group.page_size * nkv * dk)
