@@ -157,11 +157,14 @@ def test_sink_attention_parts_that_can_be_left_out():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dk", [32, 64])
 @pytest.mark.parametrize("far_key", [0, 7, 8, 15, 16, 200, 255, 256])
-def test_a_far_key_that_stands_out_is_found(dtype, far_key):
+def test_a_far_key_that_stands_out_is_found(dtype, far_key, dk):
     """One key among hundreds matches the last query strongly: the output is that key's value.
-    The key sits at the first position, at page borders (pages of 8 and multiples), far back."""
-    width, T, heads, dk, dv = 64, 300, 2, 32, 32
+    The key sits at the first position, at page borders (pages of 8 or 16 and multiples), far
+    back. Head size 64 in bfloat16 takes the tensor-memory kernel for the prompt and the
+    split-key decode kernel for the last token; everything else the CUDA-core kernel."""
+    width, T, heads, dv = 2 * dk, 300, 2, dk
     gen = torch.Generator().manual_seed(far_key)
     spec, block = attention_case(heads, heads, dk, dv, rows=6, far=20, coef=0.0, every=1, scale=1.0)
     mixer = build_mixer(spec, width, None)
@@ -171,10 +174,10 @@ def test_a_far_key_that_stands_out_is_found(dtype, far_key):
     give(mixer, W, dtype)
     x = rounded(T, width, gen=gen, std=0.05)
     mark = torch.zeros(width)
-    mark[:dk] = 1.0                                    # head 0: score 32 between the marked rows
+    mark[:dk] = 1.0                                    # head 0: score dk between the marked rows
     x[far_key] += mark
     x[T - 1] += mark
-    harness = Harness([mixer.cache_spec()], [None], dtype, num_pages=40, page_size=8)
+    harness = Harness([mixer.cache_spec()], [None], dtype, num_pages=40, page_size=8 if dk == 32 else 16)
     got = run_in_portions(mixer, harness, x, (T - 1, 1), dtype)
     want = plain.sink_attention(x, {"p." + k: v for k, v in W.items()}, "p.", block)
     assert torch.allclose(got, want, atol=2e-4 if dtype == torch.float32 else 3e-2)
@@ -184,7 +187,7 @@ def test_a_far_key_that_stands_out_is_found(dtype, far_key):
 @pytest.mark.parametrize("heads,kv,d", [(4, 2, 64), (8, 2, 128), (2, 2, 128)])
 def test_sink_attention_on_the_tensor_memory_kernel(heads, kv, d):
     """bfloat16, equal key and value widths of 64 or 128: long rows run on the tensor-memory
-    kernel, short ones beside them on the CUDA cores with their keys cut into segments. The bias
+    kernel, requests that bring up to four tokens beside them on the split-key decode kernels. The bias
     changes within the first 90 positions back, so tiles near the diagonal look it up and tiles
     beyond add its last value; two requests of one batch, one long and one short row."""
     gen = torch.Generator().manual_seed(d + heads)

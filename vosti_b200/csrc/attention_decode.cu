@@ -337,7 +337,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       for (int row = cw; row < group; row += CONSUMERS) {
         const int h = p_g * group + row;
         merge_segments<true>(partial + ((int64_t)p_item * nq + h) * max_segments * record_floats(d), out + ((int64_t)p_t * nq + h) * d,
-                       p_first, p_last, d);
+                       p_first, p_last, d, fused.sink == nullptr ? -INFINITY : fused.sink[h] * LOG2E);
       }
     }
   };
@@ -435,7 +435,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       }
 
       attend_tile<DMAX, Q_IN_REGISTERS>(ks, vs, qa, q_s, q_pitch, d, key0, kstart, pos, scale_log2, upper_rows_live, k_lane, k_xor,
-                                        v_lane, v_xor, m_row, l_row, o);
+                                        v_lane, v_xor, m_row, l_row, o,
+                                        fused.score_bias == nullptr ? nullptr : fused.score_bias + (int64_t)(g * group + min(lane >> 2, group - 1)) * (fused.score_bias_last + 1),
+                                        fused.score_bias == nullptr ? nullptr : fused.score_bias + (int64_t)(g * group + min((lane >> 2) + 8, group - 1)) * (fused.score_bias_last + 1),
+                                        fused.score_bias_last);
       __syncwarp();                                  // every lane is done with this slot: refill it
       if (edge) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       if (requested < tiles) {
@@ -808,6 +811,25 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
   return launch_decode(q, k_cache, v_cache, out, scratch, scratch_elems, arrivals, token_list, count, tokens_total, positions,
                        request_of, block_table, max_pages, page_size, num_pages, nq, nkv, d, max_kv_len, scale, window,
                        status, stream, none);
+}
+
+// The same with a distance bias (float32 [nq][bias_last + 1], base-2 units, by min(distance,
+// bias_last); or null) added to the scaled scores and a sink logit per head (float32 [nq], natural
+// units; or null) in the denominator: see attention_sink.cu for their meaning.
+VOSTI_API int vosti_attention_decode_biased(const void* q, const void* k_cache, const void* v_cache, void* out, float* scratch,
+                                            int64_t scratch_elems, int* arrivals, const int* token_list, int count,
+                                            int tokens_total, const int* positions, const int* request_of,
+                                            const int* block_table, int max_pages, int page_size, int num_pages, int nq,
+                                            int nkv, int d, int max_kv_len, float scale, int window, const float* bias,
+                                            int bias_last, const float* sink, unsigned* status, cudaStream_t stream) {
+  VOSTI_REQUIRE(bias == nullptr || bias_last >= 0, "attention_decode: bad bias table");
+  FusedProjection extras = {};
+  extras.score_bias = bias;
+  extras.score_bias_last = bias_last;
+  extras.sink = sink;
+  return launch_decode(q, k_cache, v_cache, out, scratch, scratch_elems, arrivals, token_list, count, tokens_total, positions,
+                       request_of, block_table, max_pages, page_size, num_pages, nq, nkv, d, max_kv_len, scale, window,
+                       status, stream, extras);
 }
 
 // The fused form: `partial` holds the QKV projection's K-split partial sums of the step's tokens

@@ -51,9 +51,11 @@ __host__ __device__ inline int record_floats(int d) { return d + 4; }
 // up to BATCH segments are in flight together.
 // GLOBAL: the records were written by other CTAs to global memory (read past L1); else they lie in
 // this CTA's shared memory.
+// `sink_l2` (base-2 units; -inf: none) is a logit without key or value that joins the denominator
+// once: it may raise the reference maximum and adds exp2(sink - max) to the sum.
 template <bool GLOBAL>
 __device__ __forceinline__ void merge_segments(const float* __restrict__ base, bf16* __restrict__ dst, int first,
-                                               int last, int d) {
+                                               int last, int d, float sink_l2 = -INFINITY) {
   auto load2 = [](const float* p) { return GLOBAL ? __ldcg(reinterpret_cast<const float2*>(p)) : *reinterpret_cast<const float2*>(p); };
   auto load4 = [](const float* p) { return GLOBAL ? __ldcg(reinterpret_cast<const float4*>(p)) : *reinterpret_cast<const float4*>(p); };
   const int lane = threadIdx.x & 31;
@@ -84,8 +86,9 @@ __device__ __forceinline__ void merge_segments(const float* __restrict__ base, b
     m = fmaxf(m, ml.x);
   }
   m = warp_max(m);
+  if (sink_l2 > -INFINITY) m = fmaxf(m, sink_l2);
   // pass 2: weights, sum and accumulator
-  float l = 0.f;
+  float l = sink_l2 > -INFINITY ? fast_exp2(sink_l2 - m) : 0.f;
   float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
   for (int s0 = first; s0 <= last; s0 += 32) {
     const int mine = s0 + lane;
@@ -130,7 +133,10 @@ __device__ __forceinline__ void attend_tile(uint32_t ks, uint32_t vs, const uint
                                             const uint8_t* q_s, int q_pitch, int d, int key0, int kstart, int pos,
                                             float scale_log2, bool upper_rows_live, uint32_t k_lane, uint32_t k_xor,
                                             uint32_t v_lane, uint32_t v_xor, float (&m_row)[2], float (&l_row)[2],
-                                            float (&o)[DMAX / 8][4]) {
+                                            float (&o)[DMAX / 8][4], const float* __restrict__ bias0 = nullptr,
+                                            const float* __restrict__ bias1 = nullptr, int bias_last = 0) {
+  // bias0 / bias1 (or null): the rows of a distance-bias table (base-2 units) of this lane's two
+  // query heads, indexed by min(pos - key, bias_last) and added to the scaled score
   const int lane = threadIdx.x & 31;
   // ---- S = Q K^T for 16 keys: two 8-key column tiles
   float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -158,6 +164,10 @@ __device__ __forceinline__ void attend_tile(uint32_t ks, uint32_t vs, const uint
     for (int e = 0; e < 4; ++e) {
       const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
       const bool visible = key >= kstart && key <= pos;
+      if (bias0 != nullptr) {
+        const int back = min(max(pos - key, 0), bias_last);
+        s[nt][e] = visible ? fmaf(s[nt][e], scale_log2, (e >> 1) ? bias1[back] : bias0[back]) : -INFINITY;
+      } else
       s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
       tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[nt][e]);
     }
@@ -217,6 +227,10 @@ struct FusedProjection {
   long long num_slots;
   bf16* k_cache;
   bf16* v_cache;
+  // additions to the scores, for mixers that have them (all null / 0 otherwise; they do not need `partial`)
+  const float* score_bias;     // [nq][score_bias_last + 1] float32, base-2 units, by min(distance, last)
+  int score_bias_last;
+  const float* sink;           // [nq] float32, natural units: a logit in the denominator without key or value
 };
 
 constexpr int ONCE_MAX_SEGMENTS = 16;     // CTAs per cluster of that kernel (above 8 it opts in to non-portable sizes)

@@ -324,7 +324,10 @@ attention_decode_once_kernel(const __grid_constant__ CUtensorMap map_k, const __
         __syncwarp();
       }
       attend_tile<DMAX, Q_IN_REGISTERS>(ks, vs, qa, q_s, q_pitch, d, key0, kstart, pos, scale_log2, upper_rows_live, k_lane, k_xor,
-                                        v_lane, v_xor, m_row, l_row, o);
+                                        v_lane, v_xor, m_row, l_row, o,
+                                        fused.score_bias == nullptr ? nullptr : fused.score_bias + (int64_t)(g * group + min(lane >> 2, group - 1)) * (fused.score_bias_last + 1),
+                                        fused.score_bias == nullptr ? nullptr : fused.score_bias + (int64_t)(g * group + min((lane >> 2) + 8, group - 1)) * (fused.score_bias_last + 1),
+                                        fused.score_bias_last);
       __syncwarp();                                    // every lane is done with this slot: refill it
       if (edge) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       if (requested < tiles) request_tile();
@@ -393,7 +396,8 @@ attention_decode_once_kernel(const __grid_constant__ CUtensorMap map_k, const __
   // ---- the cluster's first CTA: all segments have arrived; merge them in segment order
   if (!mb_wait_cluster(smem_addr(&records_bar), 0, status)) return;
   for (int row = cw; row < group; row += CONSUMERS)
-    merge_segments<false>(records + (int64_t)row * segments * grec, out + ((int64_t)t * nq + g * group + row) * d, p_first, p_last, d);
+    merge_segments<false>(records + (int64_t)row * segments * grec, out + ((int64_t)t * nq + g * group + row) * d, p_first, p_last, d,
+                          fused.sink == nullptr ? -INFINITY : fused.sink[g * group + row] * LOG2E);
 }
 
 // How many clusters of `cluster` CTAs with `smem` bytes each the GPU can run at once (0: none, or

@@ -745,7 +745,6 @@ def qkv_store(qkv: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optio
     return q
 
 
-SINK_DECODE_ON_CORES = _os.environ.get("VOSTI_SINK_DECODE_ON_CORES", "0") == "1"   # decode steps off the tensor-memory kernel
 SINK_SEGMENT = int(_os.environ.get("VOSTI_SINK_SEGMENT", "256"))          # keys per segment when few query rows share the GPU
 SINK_SPLIT_MAX_ROWS = 2048  # (token, head) rows up to which the keys are cut into segments
 
@@ -773,9 +772,10 @@ def attention_sink(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     table float32 [nq, distances] (base-2 units, the last column serving every larger distance)
     and an optional sink logit per head (float32 [nq], natural units). Returns [tokens, nq * dv].
     bfloat16 with equal key and value widths of 64 or 128 (pages of a multiple of 16 tokens, at
-    most 16 query heads per kv head): every row of the step, long or a single token, runs on the
-    tensor-memory kernel, whose rows are independent of one another. Everything else runs on the
-    CUDA-core kernel, with the keys cut into segments when the step has few rows."""
+    most 16 query heads per kv head): long rows run on the tensor-memory kernel and requests that
+    bring a few tokens on the split-key decode kernels, as Qwen3's do, both with the bias and the
+    sink. Everything else runs on the CUDA-core kernel, with the keys cut into segments when the
+    step has few rows."""
     _contig(q, k_cache, v_cache, bias, sink)
     tokens = q.shape[0]
     out = torch.empty((tokens, nq * dv), dtype=q.dtype, device=q.device)
@@ -783,15 +783,31 @@ def attention_sink(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     lib = library()
     tensor_memory = (q.dtype == torch.bfloat16 and dk == dv and nq // nkv <= 16
                      and lib.vosti_attention_prefill_tc_supported(dk, group.page_size))
-    if not tensor_memory or (SINK_DECODE_ON_CORES and ctx.all_decode):
+    if not tensor_memory or getattr(ctx, "layout", None) is None or "attention" not in ctx.layout:
         _attention_sink_rows(ctx, q, k_cache, v_cache, out, group, token_list=None, count=tokens, **common)
         return out
+    # as for `attention`: requests that bring a few tokens one query at a time with split keys,
+    # longer portions tile by tile on the tensor-memory kernel (the step's work lists)
+    lists = ctx.layout["attention"]
     num_pages = k_cache.numel() // (group.page_size * nkv * dk)
-    _check(lib.vosti_attention_prefill_tc_biased(
-        _p(q), _p(k_cache), _p(v_cache), _p(out), None, ctx.num_requests,
-        _p(ctx.cu_q), _p(ctx.kv_len), _p(group.block_table), group.block_table.shape[1], group.page_size, num_pages, nq,
-        nkv, dk, ctx.max_q_len, tokens, ctypes.c_float(scale), window, _p(bias),
-        0 if bias is None else bias.shape[1] - 1, _p(sink), _p(ctx.status), _stream()), "attention_prefill_tc_biased")
+    bias_last = 0 if bias is None else bias.shape[1] - 1
+    if lists["num_short_tokens"]:
+        count = lists["num_short_tokens"]
+        lib.vosti_attention_decode_scratch.restype = ctypes.c_int64
+        scratch = _workspace(q.device, lib.vosti_attention_decode_scratch(count, nq, nkv, dk, ctx.max_kv_len))
+        arrivals = _counters(q.device, count * nkv)
+        _check(lib.vosti_attention_decode_biased(
+            _p(q), _p(k_cache), _p(v_cache), _p(out), _p(scratch), ctypes.c_int64(scratch.numel()), _p(arrivals),
+            _p(ctx.extras.get("attention.short_tokens")), count, tokens, _p(ctx.positions), _p(ctx.request_of),
+            _p(group.block_table), group.block_table.shape[1], group.page_size, num_pages, nq, nkv, dk, ctx.max_kv_len,
+            ctypes.c_float(scale), window, _p(bias), bias_last, _p(sink), _p(ctx.status), _stream()),
+            "attention_decode_biased")
+    if lists["num_long_rows"]:
+        _check(lib.vosti_attention_prefill_tc_biased(
+            _p(q), _p(k_cache), _p(v_cache), _p(out), _p(ctx.extras.get("attention.long_rows")), lists["num_long_rows"],
+            _p(ctx.cu_q), _p(ctx.kv_len), _p(group.block_table), group.block_table.shape[1], group.page_size, num_pages,
+            nq, nkv, dk, lists["max_long_q_len"], tokens, ctypes.c_float(scale), window, _p(bias), bias_last, _p(sink),
+            _p(ctx.status), _stream()), "attention_prefill_tc_biased")
     return out
 
 
