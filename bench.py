@@ -410,12 +410,45 @@ def design_engine(kind, size, max_batch):
     return engine
 
 
-def design_main(args) -> int:
-    """Prefill and decode of the Mugizen design beside Qwen3 at equal sizes; one JSON line."""
+def design_one(args, name, kind) -> dict:
+    """One model (a size and a design) in this process: prefill, decode at batch 8 and 1."""
     import torch
 
-    peaks, peak_kind = load_peaks()
+    peaks, _ = load_peaks()
     torch.cuda.set_device(0)
+    size = DESIGN_SIZES[name]
+    print(f"[bench] {name}: {kind}: building", file=sys.stderr, flush=True)
+    engine = design_engine(kind, size, 8)
+    runner = engine.runner
+    weight_bytes = runner.model.weight_bytes()
+    kv_bytes = runner.cache.bytes_per_token()
+    state_bytes = sum(c.state[0].numel() * c.state.element_size() for c in runner.cache.layer_caches if c.state is not None)
+    print(f"[bench] {name}: {kind}: prefill", file=sys.stderr, flush=True)
+    prefill_ms = prefill_run(engine, 3, seed=11)
+    tflops = design_flops(size, CONTEXT, kind) / (prefill_ms * 1e-3) / 1e12
+    entry = {"prefill_tok_s": round(CONTEXT * 1e3 / prefill_ms, 1), "prefill_ms": round(prefill_ms, 3),
+             "prefill_frac_of_bf16_peak": round(tflops / peaks["bf16_tflops"], 4),
+             "weight_bytes": int(weight_bytes), "kv_bytes_per_token": int(kv_bytes), "state_bytes": int(state_bytes)}
+    for batch in (8, 1):
+        print(f"[bench] {name}: {kind}: decode at batch {batch}", file=sys.stderr, flush=True)
+        run = decode_run(engine, batch, args.steps, args.warmup, seed=21 + batch, least_repeats=3)
+        step_bytes = weight_bytes + batch * (run["context"] * kv_bytes + 2 * state_bytes)
+        entry[f"decode_b{batch}"] = {
+            "tok_s": round(batch * 1e3 / run["device_ms"], 1), "ms_per_step": round(run["device_ms"], 4),
+            "e2e_tok_s": round(batch * 1e3 / run["wall_ms"], 1), "launches_per_step": run["launches"] / args.steps,
+            "frac_of_hbm_peak": round(step_bytes / (run["device_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
+    return entry
+
+
+def design_main(args) -> int:
+    """Prefill and decode of the Mugizen design beside Qwen3 at equal sizes; one JSON line. Every
+    model is measured in a process of its own (this program started again with --design-one), so
+    that no model's scratch buffers, graphs or allocator state reach the next one's timings."""
+    if args.design_one:
+        name, kind = args.design_one.split(":")
+        print(json.dumps(design_one(args, name, kind)))
+        return 0
+    _, peak_kind = load_peaks()
     out = {}
     for name in args.design_sizes.split(","):
         size = DESIGN_SIZES[name]
@@ -423,27 +456,14 @@ def design_main(args) -> int:
         for kind in ("mugizen", "qwen3"):
             if kind == "qwen3" and size["moe"]:
                 continue                      # the engine has no other model with experts to stand beside
-            engine = design_engine(kind, size, 8)
-            runner = engine.runner
-            weight_bytes = runner.model.weight_bytes()
-            kv_bytes = runner.cache.bytes_per_token()
-            state_bytes = sum(c.state[0].numel() * c.state.element_size() for c in runner.cache.layer_caches
-                              if c.state is not None)
-            prefill_ms = prefill_run(engine, 3, seed=11)
-            tflops = design_flops(size, CONTEXT, kind) / (prefill_ms * 1e-3) / 1e12
-            entry = {"prefill_tok_s": round(CONTEXT * 1e3 / prefill_ms, 1), "prefill_ms": round(prefill_ms, 3),
-                     "prefill_frac_of_bf16_peak": round(tflops / peaks["bf16_tflops"], 4),
-                     "weight_bytes": int(weight_bytes), "kv_bytes_per_token": int(kv_bytes), "state_bytes": int(state_bytes)}
-            for batch in (8, 1):
-                run = decode_run(engine, batch, args.steps, args.warmup, seed=21 + batch, least_repeats=3)
-                step_bytes = weight_bytes + batch * (run["context"] * kv_bytes + 2 * state_bytes)
-                entry[f"decode_b{batch}"] = {
-                    "tok_s": round(batch * 1e3 / run["device_ms"], 1), "ms_per_step": round(run["device_ms"], 4),
-                    "e2e_tok_s": round(batch * 1e3 / run["wall_ms"], 1), "launches": run["launches"],
-                    "frac_of_hbm_peak": round(step_bytes / (run["device_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
-            row[kind] = entry
-            del engine, runner
-            torch.cuda.empty_cache()
+            child = subprocess.run([sys.executable, os.path.abspath(__file__), "--design", args.design, "--design-one",
+                                    f"{name}:{kind}", "--steps", str(args.steps), "--warmup", str(args.warmup),
+                                    "--context", str(CONTEXT), "--page", str(PAGE)],
+                                   stdout=subprocess.PIPE, text=True, timeout=900)
+            lines = [line for line in child.stdout.splitlines() if line.startswith("{")]
+            if child.returncode != 0 or not lines:
+                raise RuntimeError(f"measuring {kind} at size {name} failed (exit code {child.returncode})")
+            row[kind] = json.loads(lines[-1])
         out[name] = {"sizes": {k: v for k, v in size.items()}, **row}
     print(json.dumps({"design": "mugizen", "beside": "qwen3 at equal sizes", "context": CONTEXT, "page_size": PAGE,
                       "steps": args.steps, "warmup": args.warmup, "dtype": "bf16", "peaks": peak_kind,
@@ -476,6 +496,7 @@ def main() -> int:
     parser.add_argument("--design", default="", choices=["", "mugizen"],
                         help="measure this design beside Qwen3 at equal layer sizes instead of the headline")
     parser.add_argument("--design-sizes", default="s,m,moe", help="which of the sizes s, m, moe (comma-separated)")
+    parser.add_argument("--design-one", default="", help=argparse.SUPPRESS)      # size:design, one model in this process
     args = parser.parse_args()
 
     if args.gpus != 1:

@@ -192,7 +192,7 @@ def test_sink_attention_on_the_tensor_memory_kernel(heads, kv, d):
     beyond add its last value; two requests of one batch, one long and one short row."""
     gen = torch.Generator().manual_seed(d + heads)
     width, T = 96, 600
-    spec, block = attention_case(heads, kv, d, d, rows=12, far=90, coef=0.4, every=64, scale=d ** -0.5)
+    spec, block = attention_case(heads, kv, d, d, rows=12, far=90, coef=0.4, every=50, scale=d ** -0.5)
     mixer = build_mixer(spec, width, None)
     W = attention_weights(mixer, width, gen, spread=1.5)
     give(mixer, W, torch.bfloat16)
