@@ -391,7 +391,7 @@ def close_rows(got, want, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["p", "q"])
+@pytest.mark.parametrize("name", ["p", "q", "r"])
 def test_whole_prompt_portions_and_decoding_against_plain(models, name, dtype, monkeypatch):
     from vosti_b200.parts import ExpertMixture
     monkeypatch.setattr(ExpertMixture, "GROUPED_FROM", 16)      # portions of 16 tokens or more sort their pairs by expert
@@ -400,7 +400,8 @@ def test_whole_prompt_portions_and_decoding_against_plain(models, name, dtype, m
     want = plain.forward(config, W, tokens)
     everything = list(range(len(tokens)))
     for sizes in ((61,), (29,) + (1,) * 32, (2, 5, 1, 1, 17, 2, 3, 30)):
-        runner = ModelRunner(folder, dtype=dtype, num_pages=12, page_size=8, max_requests=2)
+        page = tiny.PAGE[name]
+        runner = ModelRunner(folder, dtype=dtype, num_pages=96 // page, page_size=page, max_requests=2)
         runner.begin("r")
         rows, at = [], 0
         for size in sizes:
@@ -431,15 +432,17 @@ def test_residual_stream_after_every_layer_run(models):
         assert torch.allclose(got, expected, atol=2e-4, rtol=2e-4)
 
 
-@pytest.mark.parametrize("name", ["p", "q"])
-def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(models, name):
+@pytest.mark.parametrize("name,dtype", [("p", "float32"), ("q", "float32"), ("r", "float32"), ("r", "bfloat16")])
+def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(models, name, dtype):
     """Four requests through two state slots and a pool that holds two of them: portions of some
     beside single tokens of others; every request equals itself alone."""
     folder, config, W = models[name]
     lengths = {"a": 37, "b": 9, "c": 1, "d": 26}
     tokens = {r: prompt(config, n, 10 + i) for i, (r, n) in enumerate(lengths.items())}
     want = {r: plain.forward(config, W, t) for r, t in tokens.items()}
-    runner = ModelRunner(folder, dtype="float32", num_pages=10, page_size=8, max_requests=2)
+    page = tiny.PAGE[name]
+    pool = 80 // page
+    runner = ModelRunner(folder, dtype=dtype, num_pages=pool, page_size=page, max_requests=2)
     schedule = [
         [("a", 5), ("b", 2)], [("a", 1), ("b", 6)], [("b", 1), ("a", 20)], [("a", 1)],      # b ends in step 2
         [("c", 1), ("a", 2)], [("d", 3), ("a", 8)], [("d", 1)], [("d", 22)],                # c, then a end
@@ -464,8 +467,8 @@ def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(models, n
     runner.cache.check()
     for r in lengths:
         assert at[r] == lengths[r]
-        assert close_rows(torch.cat(got[r]), want[r], "float32"), r
-    assert runner.cache.available_pages() == 10 and len(runner.cache.free_slots) == 2
+        assert close_rows(torch.cat(got[r]), want[r], dtype), r
+    assert runner.cache.available_pages() == pool and len(runner.cache.free_slots) == 2
 
 
 def test_long_decoding_keeps_its_state(models):

@@ -7,6 +7,8 @@ P: odd sizes everywhere; key and value widths differ; fewer key/value heads than
    of bias rows; temperatures that change every 5 positions.
 Q: no loop; a convolution of one tap (no tail in the state); one expert; two bias rows;
    one head; a key width that needs two lanes per column in the recurrence.
+R: attention heads of 64 with equal key and value widths and pages of 16 tokens, which in
+   bfloat16 run on the tensor-memory and split-key decode kernels; a loop from the first layer.
 """
 import json
 from pathlib import Path
@@ -48,7 +50,15 @@ Q = dict(architecture="Mugizen", vocab=128, width=64, norm=dict(eps=1e-5), loop=
 ])
 Q_SHAPES = dict(bias_rows=2, decay_rank=2, gate_rank=9)
 
-ALL = {"p": (P, P_SHAPES, 11), "q": (Q, Q_SHAPES, 12)}
+R = dict(architecture="Mugizen", vocab=160, width=128, norm=dict(eps=1e-6), loop=dict(start=0, stop=1, times=2), layers=[
+    _layer(_left(4, 2, 64, 64, 0.125, 50, 0.3, 16), _right(4, 2, 24, 32, 3),
+           dict(kind="moe", expert=dict(ff=32), router=dict(experts=4, top=2))),
+    _layer(_left(2, 2, 64, 64, 0.125, 50, 0.3, 16), _right(2, 1, 32, 64, 4), dict(kind="dense", ff=192)),
+])
+R_SHAPES = dict(bias_rows=8, decay_rank=8, gate_rank=8)
+
+ALL = {"p": (P, P_SHAPES, 11), "q": (Q, Q_SHAPES, 12), "r": (R, R_SHAPES, 13)}
+PAGE = {"p": 8, "q": 8, "r": 16}
 
 
 def draw(name, shape, gen):
