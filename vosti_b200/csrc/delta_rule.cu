@@ -333,7 +333,14 @@ VOSTI_API int vosti_delta_prep(const void* proj, int proj_f32, int stride, int o
   const int cc = 2 * kv_heads * dk + heads * dv;
   const size_t smem = (size_t)cc * sizeof(float);
   VOSTI_REQUIRE(smem <= 200 * 1024, "delta_prep: %d channels do not fit shared memory", cc);
-  if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  {
+    // once, to the most a launch may ask for: the attribute is not touched while launches are in flight
+    static bool configured = false;
+    if (!configured) {
+      cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      configured = true;
+    }
+  }
   vosti_launch(delta_prep_kernel, dim3(tokens), dim3(256), smem, stream, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { vosti_set_error("%s", cudaGetErrorString(e)); return (int)e; }
@@ -378,7 +385,12 @@ VOSTI_API int vosti_delta_scan(const float* q, const float* k, const float* v, c
   const size_t smem = 2 * (size_t)(TOKENS * (3 * ks * rows + cols) + TOKENS) * sizeof(float);
 #define VOSTI_SCAN(KS, R)                                                                                           \
   do {                                                                                                              \
-    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<KS, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    static bool configured = false;    /* once per instantiation, to the most a launch of it may ask for */           \
+    if (!configured) {                                                                                              \
+      cudaFuncSetAttribute(delta_scan_kernel<KS, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,                   \
+                           (int)(2 * (size_t)(TOKENS * (3 * KS * R + SCAN_THREADS / KS) + TOKENS) * sizeof(float))); \
+      configured = true;                                                                                            \
+    }                                                                                                               \
     vosti_launch(delta_scan_kernel<KS, R>, grid, dim3(threads), smem, stream, q, k, v, beta, decay, out, state,    \
                  state_stride, cu_q, state_slots, num_slots, kv_heads, heads, dk, dv);                              \
   } while (0)
