@@ -4,9 +4,11 @@ from .registry import (architecture_of, known_architectures, model_spec_from_con
 from . import qwen3 as _qwen3
 from .qwen3 import Qwen3Config
 from . import mugizen as _mugizen
+from . import vivesun as _vivesun
 
 register_architecture(_qwen3.ARCHITECTURE, _qwen3.spec_from_config, replace=True)
 register_architecture(_mugizen.ARCHITECTURE, _mugizen.spec_from_config, replace=True)
+register_architecture(_vivesun.ARCHITECTURE, _vivesun.spec_from_config, replace=True)
 
 __all__ = [
     "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "Qwen3Config",

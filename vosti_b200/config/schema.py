@@ -60,6 +60,7 @@ class LayerSpec:
     position: Optional[PartSpec]
     arrangement: str = "pre_norm"
     names: Tuple[Tuple[str, str], ...] = ()
+    token_input: Optional[PartSpec] = None      # a sublayer that reads the token ids again (arrangements that take one)
 
     def name_of(self, role: str) -> str:
         for key, value in self.names:

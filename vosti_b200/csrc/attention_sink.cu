@@ -1,5 +1,9 @@
-// Paged causal attention without rotation, with three optional additions, and key and value
-// heads of different widths:
+// Paged causal attention with optional additions, and key and value heads of different widths:
+//   * a rotation of the first 2 * rot_half elements of every query and key head, in pairs
+//     (i, i + rot_half), by the angle position * freq[i] formed in float32 (no table, so no limit
+//     on positions);
+//   * a chunked mask instead of a window: a query sees the keys of its own chunk of positions
+//     only (handed down as a negative window, see first_visible_key);
 //   * a query temperature: the query at position p is multiplied by
 //     1 + coef * ln(floor((p + 1) / every) + 1);
 //   * a learned bias per (distance, head) added to the scaled score. The host hands a table
@@ -63,7 +67,9 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                  const int* __restrict__ positions, const int* __restrict__ slot_mapping, int64_t num_slots,
-                 int page_size, int nq, int nkv, int dk, int dv, float temp_coef, int temp_every, unsigned* status) {
+                 int page_size, int nq, int nkv, int dk, int dv, float temp_coef, int temp_every, unsigned* status,
+                 const float* __restrict__ freq, int rot_half) {
+  extern __shared__ float turn[];            // [2 * rot_half]: cosines, then sines, of this token's angles
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -71,8 +77,25 @@ qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict
   const T* row = qkv + (int64_t)t * (wq + wk + wv);
   float temp = 1.f;
   if (temp_coef != 0.f) temp = 1.f + temp_coef * logf((float)((positions[t] + 1) / temp_every + 1));
+  if (rot_half > 0) {
+    const float p = (float)positions[t];
+    for (int i = threadIdx.x; i < rot_half; i += blockDim.x) {
+      const float angle = p * freq[i];
+      turn[i] = cosf(angle);
+      turn[rot_half + i] = sinf(angle);
+    }
+    __syncthreads();
+  }
+  // element i of a row of heads of width dk, turned if it lies in the rotated part of its head
+  auto turned = [&](const T* src, int i) {
+    const int j = i % dk;
+    const float x = to_f32(src[i]);
+    if (j < rot_half) return x * turn[j] - to_f32(src[i + rot_half]) * turn[rot_half + j];
+    if (j < 2 * rot_half) return x * turn[j - rot_half] + to_f32(src[i - rot_half]) * turn[j];
+    return x;
+  };
   // bfloat16 rows whose widths allow it move as 16-byte words (8 elements)
-  const bool vec = sizeof(T) == 2 && dk % 8 == 0 && dv % 8 == 0;
+  const bool vec = rot_half == 0 && sizeof(T) == 2 && dk % 8 == 0 && dv % 8 == 0;
   if (vec) {
     const uint4* src = reinterpret_cast<const uint4*>(row);
     uint4* dst = reinterpret_cast<uint4*>(q_out + (int64_t)t * wq);
@@ -89,7 +112,7 @@ qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict
       dst[i] = raw;
     }
   } else {
-    for (int i = threadIdx.x; i < wq; i += blockDim.x) q_out[(int64_t)t * wq + i] = from_f32<T>(to_f32(row[i]) * temp);
+    for (int i = threadIdx.x; i < wq; i += blockDim.x) q_out[(int64_t)t * wq + i] = from_f32<T>(turned(row, i) * temp);
   }
   if (k_cache == nullptr) return;
   const int64_t slot = slot_mapping[t];
@@ -113,7 +136,7 @@ qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict
   }
   for (int i = threadIdx.x; i < wk; i += blockDim.x) {
     const int g = i / dk, c = i % dk;
-    k_cache[((page * nkv + g) * page_size + offset) * dk + c] = row[wq + i];
+    k_cache[((page * nkv + g) * page_size + offset) * dk + c] = rot_half > 0 ? from_f32<T>(turned(row + wq, i)) : row[wq + i];
   }
   for (int i = threadIdx.x; i < wv; i += blockDim.x) {
     const int g = i / dv, c = i % dv;
@@ -145,7 +168,7 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
 
   const int b = request_of[t];
   const int pos = positions[t];
-  int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  int kstart = first_visible_key(pos, window);
   int kend = pos;                                   // inclusive
   if (partial != nullptr) {                         // this warp's segment of the keys (segment: a multiple of 32)
     kstart = max(kstart, (int)blockIdx.y * segment);
@@ -292,17 +315,22 @@ attention_sink_merge_kernel(const float* __restrict__ partial, int segments, T* 
 VOSTI_API int vosti_qkv_store(const void* qkv, void* q_out, void* k_cache, void* v_cache, const int* positions,
                               const int* slot_mapping, int64_t num_slots, int page_size, int tokens, int nq, int nkv,
                               int dk, int dv, float temp_coef, int temp_every, int is_f32, unsigned* status,
-                              cudaStream_t stream) {
+                              const float* freq, int rot_half, cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && nq > 0 && nkv >= 0 && dk > 0 && dv > 0, "qkv_store: bad sizes");
   VOSTI_REQUIRE(temp_coef == 0.f || (temp_every > 0 && positions != nullptr), "qkv_store: the temperature needs positions and a positive period");
   VOSTI_REQUIRE(k_cache == nullptr || (v_cache != nullptr && slot_mapping != nullptr && page_size > 0), "qkv_store: a cache needs slots");
+  VOSTI_REQUIRE(rot_half >= 0 && 2 * rot_half <= dk && (rot_half == 0 || (freq != nullptr && positions != nullptr)),
+                "qkv_store: the rotation takes at most the whole head and needs frequencies and positions");
   if (tokens == 0) return VOSTI_OK;
+  const size_t turn_bytes = (size_t)2 * rot_half * sizeof(float);
   if (is_f32)
-    vosti_launch(qkv_store_kernel<float>, dim3(tokens), dim3(256), 0, stream, (const float*)qkv, (float*)q_out, (float*)k_cache,
-                 (float*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, dk, dv, temp_coef, temp_every, status);
+    vosti_launch(qkv_store_kernel<float>, dim3(tokens), dim3(256), turn_bytes, stream, (const float*)qkv, (float*)q_out, (float*)k_cache,
+                 (float*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, dk, dv, temp_coef, temp_every, status, freq,
+                 rot_half);
   else
-    vosti_launch(qkv_store_kernel<bf16>, dim3(tokens), dim3(256), 0, stream, (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache,
-                 (bf16*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, dk, dv, temp_coef, temp_every, status);
+    vosti_launch(qkv_store_kernel<bf16>, dim3(tokens), dim3(256), turn_bytes, stream, (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache,
+                 (bf16*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, dk, dv, temp_coef, temp_every, status, freq,
+                 rot_half);
   VOSTI_LAUNCH_CHECK();
 }
 
@@ -320,7 +348,7 @@ VOSTI_API int vosti_attention_sink(const void* q, const void* k_cache, const voi
   VOSTI_REQUIRE(tokens >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention: bad head counts nq=%d nkv=%d", nq, nkv);
   VOSTI_REQUIRE(dk > 0 && dv > 0 && dk <= MAX_W && dv <= MAX_W, "attention: head widths %d / %d must be at most %d", dk, dv, MAX_W);
   VOSTI_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0, "attention: bad cache geometry");
-  VOSTI_REQUIRE(window >= 0 && (bias == nullptr || bias_last >= 0), "attention: bad window or bias table");
+  VOSTI_REQUIRE(bias == nullptr || bias_last >= 0, "attention: bad bias table");       // (window < 0: a chunk)
   VOSTI_REQUIRE(segments >= 1 && segments <= 65535 && (segments == 1 || (scratch != nullptr && segment > 0 && segment % 32 == 0)),
                 "attention: key segments need scratch and a length that is a multiple of 32");
   if (tokens == 0) return VOSTI_OK;

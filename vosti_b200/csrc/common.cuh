@@ -102,6 +102,15 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return total;
 }
 
+// First key a query at position `pos` may see. `window` > 0: the last `window` keys up to its own;
+// `window` < 0: the keys of its own chunk of -window positions (chunk boundaries are the multiples of the chunk length, in absolute positions);
+// 0: every earlier key.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window) {
+  if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+  if (window < 0) return pos - pos % (-window);
+  return 0;
+}
+
 __device__ __forceinline__ void raise_fault(unsigned* status, unsigned bit) {
   if (status) atomicOr(status, bit);
 }

@@ -1,12 +1,15 @@
 // Mixture of experts: the router's choice and what it costs to apply it.
 //
 // moe_route: per token, the `top` experts with the largest float32 router logits (the lowest
-// index wins a tie) and their weights, the softmax over the chosen logits only. It writes the
+// index wins a tie) and their weights: the softmax over the chosen logits only, or (`over_all`)
+// the softmax over all experts, of which the chosen ones' scores are divided by their sum (plus
+// 1e-20); either way times a constant `scale`. It writes the
 // choice twice: as lists (expert ids and weights, [tokens, top]) and as a dense float32 matrix
 // [tokens, experts] that is zero where an expert was not chosen.
 //
 // moe_scale: multiplies each expert's slice of the stacked activation [tokens, experts * ff] by
-// the token's weight for that expert (zero for experts it did not choose), so that one product
+// the token's weight for that expert (zero for experts it did not choose), after an optional
+// activation of its own (the exact GELU, for experts without a gate), so that one product
 // with the experts' down projections side by side, [width, experts * ff], is the weighted sum
 // of the chosen experts' outputs.
 //
@@ -21,7 +24,7 @@ namespace {
 
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, int tokens, int experts, int top, int* __restrict__ chosen,
-                 float* __restrict__ weights, float* __restrict__ dense) {
+                 float* __restrict__ weights, float* __restrict__ dense, int over_all, float scale) {
   pdl_wait();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
@@ -54,7 +57,15 @@ moe_route_kernel(const float* __restrict__ logits, int tokens, int experts, int 
     }
   }
   __syncwarp();
-  const float inv = 1.f / total;
+  float inv = 1.f / total;
+  if (over_all) {
+    // scores over all experts: exp(z - max) / Z; the chosen ones' sum is total / Z
+    float z = 0.f;
+    for (int e = lane; e < experts; e += 32) z += expf(row[e] - first);
+    z = warp_sum(z);
+    inv = (1.f / z) / (total / z + 1e-20f);
+  }
+  inv *= scale;
   if (lane == 0)
     for (int r = 0; r < top; ++r) {
       const float w = weights[(int64_t)t * top + r] * inv;
@@ -63,15 +74,20 @@ moe_route_kernel(const float* __restrict__ logits, int tokens, int experts, int 
     }
 }
 
+// `dense` null: the activation alone.
 template <typename T>
-__global__ void moe_scale_kernel(T* __restrict__ act, const float* __restrict__ dense, int64_t tokens, int experts, int ff) {
+__global__ void moe_scale_kernel(T* __restrict__ act, const float* __restrict__ dense, int64_t tokens, int experts, int ff,
+                                 int gelu) {
   pdl_wait();
   pdl_launch_dependents();
   const int64_t width = (int64_t)experts * ff, n = tokens * width;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t t = i / width;
     const int e = (int)((i - t * width) / ff);
-    act[i] = from_f32<T>(to_f32(act[i]) * dense[t * experts + e]);
+    float x = to_f32(act[i]);
+    if (gelu) x = 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
+    if (dense != nullptr) x *= dense[t * experts + e];
+    act[i] = from_f32<T>(x);
   }
 }
 
@@ -149,20 +165,21 @@ VOSTI_API int vosti_moe_combine(const float* y, const int* where, const float* w
 }
 
 VOSTI_API int vosti_moe_route(const float* logits, int tokens, int experts, int top, int* chosen, float* weights,
-                              float* dense, cudaStream_t stream) {
+                              float* dense, int over_all, float scale, cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && top <= experts, "moe_route: bad sizes experts=%d top=%d", experts, top);
   VOSTI_REQUIRE(experts <= 2048, "moe_route: %d experts (at most 2048 are taken)", experts);
   if (tokens == 0) return VOSTI_OK;
-  vosti_launch(moe_route_kernel, dim3((tokens + 3) / 4), dim3(128), 0, stream, logits, tokens, experts, top, chosen, weights, dense);
+  vosti_launch(moe_route_kernel, dim3((tokens + 3) / 4), dim3(128), 0, stream, logits, tokens, experts, top, chosen, weights, dense, over_all, scale);
   VOSTI_LAUNCH_CHECK();
 }
 
-VOSTI_API int vosti_moe_scale(void* act, const float* dense, int tokens, int experts, int ff, int is_f32, cudaStream_t stream) {
+VOSTI_API int vosti_moe_scale(void* act, const float* dense, int tokens, int experts, int ff, int is_f32, int gelu,
+                              cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && experts > 0 && ff > 0, "moe_scale: bad sizes");
   if (tokens == 0) return VOSTI_OK;
   const int64_t n = (int64_t)tokens * experts * ff;
   const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-  if (is_f32) vosti_launch(moe_scale_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)act, dense, (int64_t)tokens, experts, ff);
-  else vosti_launch(moe_scale_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)act, dense, (int64_t)tokens, experts, ff);
+  if (is_f32) vosti_launch(moe_scale_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)act, dense, (int64_t)tokens, experts, ff, gelu);
+  else vosti_launch(moe_scale_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)act, dense, (int64_t)tokens, experts, ff, gelu);
   VOSTI_LAUNCH_CHECK();
 }

@@ -1,7 +1,9 @@
 // Row kernels for models that keep their residual stream in float32 whatever the serving
 // type: the deferred residual sum, Dynamic Tanh (a norm without statistics), the packing of
 // [stream ; first embedding] for a loop's re-entry product, and the merge of side-by-side
-// mixer branches (each divided by its root mean square, weighted, averaged).
+// mixer branches (each divided by its root mean square, weighted, averaged; or a plain sum with a
+// constant per branch), and the root-mean-square norm over the stream (weight stored as it is
+// or around zero).
 //
 // The stream is float32 [rows, width]. A sublayer's output ("term") is float32 or the serving
 // type; up to two terms wait to be added (mixer and feed-forward of a parallel block), and the
@@ -86,13 +88,110 @@ stream_sum_kernel(const float* stream, const void* t1, int t1_f32, const void* t
   }
 }
 
+// x = stream + t1 + t2 (any of them absent); stream_out <- x; then
+//   weight given:  out <- x / sqrt(mean(x^2) + eps) * (offset + weight)
+//   no weight:     out <- x (rounded to the output type)
+// `out` may be absent when only the sum is wanted. The row is walked twice; the second walk reads
+// the sum back from stream_out where it was stored (every thread reads what it wrote itself, so
+// stream_out may be the stream), else it forms the sum again from the same operands.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+rms_stream_kernel(const float* stream, const void* t1, int t1_f32, const void* t2, int t2_f32, float* stream_out,
+                  const void* __restrict__ weight, int w_f32, float offset, float eps, TO* out, int width) {
+  __shared__ float scratch[32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t base = (int64_t)blockIdx.x * width;
+  const bool vec = width % 4 == 0;
+  float ss = 0.f;
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+      float4 x = stream != nullptr ? *reinterpret_cast<const float4*>(stream + base + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      if (t1 != nullptr) { const float4 a = load_flex4(t1, t1_f32, base + i); x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w; }
+      if (t2 != nullptr) { const float4 a = load_flex4(t2, t2_f32, base + i); x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w; }
+      if (stream_out != nullptr) *reinterpret_cast<float4*>(stream_out + base + i) = x;
+      ss += (x.x * x.x + x.y * x.y) + (x.z * x.z + x.w * x.w);
+    }
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      float x = stream != nullptr ? stream[base + i] : 0.f;
+      x += term_at(t1, t1_f32, base + i);
+      x += term_at(t2, t2_f32, base + i);
+      if (stream_out != nullptr) stream_out[base + i] = x;
+      ss += x * x;
+    }
+  }
+  if (out == nullptr) return;
+  float inv = 1.f;
+  if (weight != nullptr) {
+    const float total = block_sum(ss, scratch);
+    inv = 1.f / sqrtf(total / (float)width + eps);
+  }
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+      float4 x;
+      if (stream_out != nullptr) {
+        x = *reinterpret_cast<const float4*>(stream_out + base + i);
+      } else {
+        x = stream != nullptr ? *reinterpret_cast<const float4*>(stream + base + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t1 != nullptr) { const float4 a = load_flex4(t1, t1_f32, base + i); x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w; }
+        if (t2 != nullptr) { const float4 a = load_flex4(t2, t2_f32, base + i); x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w; }
+      }
+      if (weight != nullptr) {
+        const float4 w = load_flex4(weight, w_f32, i);
+        x = make_float4(x.x * inv * (offset + w.x), x.y * inv * (offset + w.y), x.z * inv * (offset + w.z), x.w * inv * (offset + w.w));
+      }
+      store4(out + base + i, x);
+    }
+    return;
+  }
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float x;
+    if (stream_out != nullptr) {
+      x = stream_out[base + i];
+    } else {
+      x = stream != nullptr ? stream[base + i] : 0.f;
+      x += term_at(t1, t1_f32, base + i);
+      x += term_at(t2, t2_f32, base + i);
+    }
+    if (weight != nullptr) x = x * inv * (offset + load_flex(weight, w_f32, i));
+    out[base + i] = from_f32<TO>(x);
+  }
+}
+
 constexpr int MAX_BRANCHES = 4;
 struct Branches {
   const void* x[MAX_BRANCHES];       // [rows, width], float32 or bfloat16
   const void* w[MAX_BRANCHES];       // [width]
   int x_f32[MAX_BRANCHES];
+  float scale[MAX_BRANCHES];         // the plain sum's constant per branch
   int count;
 };
+
+// out = sum_b scale_b * x_b, float32, added in branch order.
+__global__ void __launch_bounds__(256)
+branch_sum_kernel(Branches br, float* __restrict__ out, int width) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t base = (int64_t)blockIdx.x * width;
+  if (width % 4 == 0) {
+    for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int b = 0; b < br.count; ++b) {
+        const float4 v = load_flex4(br.x[b], br.x_f32[b], base + i);
+        const float c = br.scale[b];
+        acc.x = fmaf(c, v.x, acc.x); acc.y = fmaf(c, v.y, acc.y); acc.z = fmaf(c, v.z, acc.z); acc.w = fmaf(c, v.w, acc.w);
+      }
+      *reinterpret_cast<float4*>(out + base + i) = acc;
+    }
+    return;
+  }
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float acc = 0.f;
+    for (int b = 0; b < br.count; ++b) acc = fmaf(br.scale[b], load_flex(br.x[b], br.x_f32[b], base + i), acc);
+    out[base + i] = acc;
+  }
+}
 
 // out = (1 / count) * sum_b  x_b / sqrt(mean(x_b^2) + eps) * w_b, float32.
 __global__ void __launch_bounds__(256)
@@ -186,5 +285,40 @@ VOSTI_API int vosti_branch_merge(const void* const* xs, const int* x_f32, const 
     br.x_f32[b] = x_f32[b];
   }
   vosti_launch(branch_merge_kernel, dim3(rows), dim3(256), 0, stream_id, br, w_f32, out, width, eps);
+  VOSTI_LAUNCH_CHECK();
+}
+
+// Root-mean-square norm over the float32 stream (see rms_stream_kernel); `weight` null: the sum
+// alone, rounded to the output type; `out` null: only stream_out is written.
+VOSTI_API int vosti_rms_stream(const float* stream, const void* t1, int t1_f32, const void* t2, int t2_f32, float* stream_out,
+                               const void* weight, int w_f32, float offset, float eps, void* out, int out_f32, int rows,
+                               int width, cudaStream_t stream_id) {
+  VOSTI_REQUIRE(rows >= 0 && width > 0, "rms_stream: bad sizes rows=%d width=%d", rows, width);
+  VOSTI_REQUIRE(stream != nullptr || t1 != nullptr, "rms_stream: nothing to norm");
+  VOSTI_REQUIRE(out != nullptr || stream_out != nullptr, "rms_stream: nowhere to write");
+  if (rows == 0) return VOSTI_OK;
+  if (out_f32)
+    vosti_launch(rms_stream_kernel<float>, dim3(rows), dim3(256), 0, stream_id, stream, t1, t1_f32, t2, t2_f32, stream_out,
+                 weight, w_f32, offset, eps, (float*)out, width);
+  else
+    vosti_launch(rms_stream_kernel<bf16>, dim3(rows), dim3(256), 0, stream_id, stream, t1, t1_f32, t2, t2_f32, stream_out,
+                 weight, w_f32, offset, eps, (bf16*)out, width);
+  VOSTI_LAUNCH_CHECK();
+}
+
+// out = sum_b scales[b] * x_b, float32 [rows, width].
+VOSTI_API int vosti_branch_sum(const void* const* xs, const int* x_f32, const float* scales, int count, float* out, int rows,
+                               int width, cudaStream_t stream_id) {
+  VOSTI_REQUIRE(count >= 1 && count <= MAX_BRANCHES, "branch_sum: %d branches (1 to %d are taken)", count, MAX_BRANCHES);
+  VOSTI_REQUIRE(rows >= 0 && width > 0, "branch_sum: bad sizes rows=%d width=%d", rows, width);
+  if (rows == 0) return VOSTI_OK;
+  Branches br = {};
+  br.count = count;
+  for (int b = 0; b < count; ++b) {
+    br.x[b] = xs[b];
+    br.x_f32[b] = x_f32[b];
+    br.scale[b] = scales[b];
+  }
+  vosti_launch(branch_sum_kernel, dim3(rows), dim3(256), 0, stream_id, br, out, width);
   VOSTI_LAUNCH_CHECK();
 }

@@ -35,6 +35,8 @@ class DecoderModel:
             if entry.cache_from is None and (entry.layer, entry.instance) not in self.cache_index:
                 self.cache_index[(entry.layer, entry.instance)] = len(self.cache_layers)
                 self.cache_layers.append(entry.layer)
+        # an embedding that keeps something per request gets state slots of its own, after the blocks' caches
+        self.embedding_cache = len(self.cache_layers) if self.embedding.state_spec() is not None else None
         self.device = None
         self.dtype = None
 
@@ -54,8 +56,9 @@ class DecoderModel:
 
     def cache_specs(self):
         """(paged cache spec, state spec) of every cache in `cache_layers` order."""
-        return ([self.blocks[i].mixer.cache_spec() for i in self.cache_layers],
-                [self.blocks[i].mixer.state_spec() for i in self.cache_layers])
+        own = self.embedding_cache is not None
+        return ([self.blocks[i].mixer.cache_spec() for i in self.cache_layers] + ([None] if own else []),
+                [self.blocks[i].mixer.state_spec() for i in self.cache_layers] + ([self.embedding.state_spec()] if own else []))
 
     @property
     def capture_safe(self) -> bool:
@@ -78,14 +81,22 @@ class DecoderModel:
         return name if key == "weight" else cls._prefix_of(name) + key
 
     @classmethod
+    def _part_tensor_name(cls, name: str, part, key: str) -> str:
+        """The same, unless the part's spec names the tensor outright (parameter `names`: pairs of
+        (key, checkpoint name))."""
+        named = dict(part.spec.get("names") or ())
+        return named[key] if key in named else cls._tensor_name(name, key)
+
+    @classmethod
     def _own(cls, tensors, name: str, part):
         """The tensors of a model-level part, by the part's own keys."""
-        return {key: tensors[cls._tensor_name(name, key)] for key in part.weight_specs()
-                if cls._tensor_name(name, key) in tensors}
+        return {key: tensors[cls._part_tensor_name(name, part, key)] for key in part.weight_specs()
+                if cls._part_tensor_name(name, part, key) in tensors}
 
     def expected_weights(self) -> Dict[str, WeightSpec]:
         spec = self.spec
-        out = {self._tensor_name(spec.embed_name, key): w for key, w in self.embedding.weight_specs().items()}
+        out = {self._part_tensor_name(spec.embed_name, self.embedding, key): w
+               for key, w in self.embedding.weight_specs().items()}
         for i, block in enumerate(self.blocks):
             prefix = spec.layer_prefix.format(i=i)
             for key, w in block.weight_specs().items():
@@ -168,8 +179,11 @@ class DecoderModel:
         """Run every entry of the run order over the batch in `ctx`; returns the last
         block's (hidden, residual), both [T, hidden] (residual None without blocks)."""
         source = ctx.extras.get("feedback") if ctx.extras else None
-        hidden = self.embedding.forward(ctx, ctx.tokens,
-                                        feedback=None if source is None else (source, ctx.feedback_values))
+        feedback = None if source is None else (source, ctx.feedback_values)
+        if self.embedding_cache is not None:
+            hidden = self.embedding.forward(ctx, ctx.tokens, feedback=feedback, cache=layer_caches[self.embedding_cache])
+        else:
+            hidden = self.embedding.forward(ctx, ctx.tokens, feedback=feedback)
         first = hidden                      # the embedding output, which a re-entry reads again
         residual: Optional[torch.Tensor] = None
         for entry in self.spec.run_order:

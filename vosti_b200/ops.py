@@ -724,24 +724,101 @@ def branch_merge(xs, weights, eps: float) -> torch.Tensor:
     return out
 
 
+def branch_sum(xs, scales) -> torch.Tensor:
+    """sum over branches of scales[b] * x_b, float32 [rows, width], added in branch order."""
+    xs = [materialize(x) for x in xs]
+    _contig(*xs)
+    count = len(xs)
+    rows, width = xs[0].shape
+    if len(scales) != count or any(tuple(x.shape) != (rows, width) for x in xs):
+        raise KernelError("branch_sum: branches must share a shape and have a constant each")
+    out = torch.empty((rows, width), dtype=torch.float32, device=xs[0].device)
+    x_ptrs = (ctypes.c_void_p * count)(*[x.data_ptr() for x in xs])
+    kinds = (ctypes.c_int * count)(*[_is_f32(x) for x in xs])
+    consts = (ctypes.c_float * count)(*[float(c) for c in scales])
+    _check(library().vosti_branch_sum(x_ptrs, kinds, consts, count, _p(out), rows, width, _stream()), "branch_sum")
+    return out
+
+
+def rms_stream(x, weight: Optional[torch.Tensor], eps: float, out_dtype: Optional[torch.dtype], *, offset: float = 0.0,
+               stream: Optional[torch.Tensor] = None, stream_out: Optional[torch.Tensor] = None):
+    """Root-mean-square norm of s = stream + x over a float32 residual stream (x: a tensor, a
+    `DeferredSum` or None; stream: float32 or None): s / sqrt(mean(s^2) + eps) * (offset + weight) in
+    float32, rounded to `out_dtype`; s itself goes to `stream_out` (float32, may be `stream`).
+    Without a weight the result is s rounded to `out_dtype`; without `out_dtype` only the sum is
+    stored and None is returned."""
+    terms, flat = _terms(x)
+    like = stream if stream is not None else terms[0]
+    _contig(stream, stream_out, weight)
+    if stream is not None and stream.dtype != torch.float32 or stream_out is not None and stream_out.dtype != torch.float32:
+        raise KernelError("rms_stream: the residual stream is float32")
+    rows, width = like.shape
+    out = None if out_dtype is None else torch.empty((rows, width), dtype=out_dtype, device=like.device)
+    _check(library().vosti_rms_stream(_p(stream), *flat, _p(stream_out), _p(weight), 0 if weight is None else _is_f32(weight),
+                                      ctypes.c_float(offset), ctypes.c_float(eps), _p(out),
+                                      0 if out is None else _is_f32(out), rows, width, _stream()), "rms_stream")
+    return out
+
+
+# ---------------------------------------------------------------- token inputs
+def pair_embedding(ids: torch.Tensor, table: torch.Tensor, pairs: torch.Tensor, last_token: torch.Tensor, ctx, *,
+                   buckets: int, mul_prev: int, mul_cur: int, feedback: Optional[tuple] = None):
+    """table[id] + pairs[(prev * mul_prev + id * mul_cur) % buckets] in float32, row `buckets` of
+    `pairs` for tokens at position 0; `prev` is the token before in the step, or, for the first
+    token of a request's portion, what `last_token` (int32 [slots]) holds for its slot, which is
+    then set to the portion's last token. Returns (rows float32 [tokens, hidden], the token ids
+    int32 [tokens] with those a sampler left on the device filled in)."""
+    _contig(ids, table, pairs, last_token)
+    source, values = feedback if feedback is not None else (None, None)
+    if source is not None:
+        _contig(source, values)
+    if _is_f32(table) != _is_f32(pairs) or last_token.dtype != torch.int32 or pairs.shape[0] != buckets + 1:
+        raise KernelError("pair_embedding: the tables must share a type, the pair table has buckets + 1 rows")
+    tokens = ids.shape[0]
+    out = torch.empty((tokens, table.shape[1]), dtype=torch.float32, device=table.device)
+    resolved = torch.empty((tokens,), dtype=torch.int32, device=table.device)
+    _check(library().vosti_pair_embedding(
+        _p(ids), _p(source), _p(values), _p(ctx.positions), _p(ctx.request_of), _p(ctx.cu_q), _p(ctx.state_slots),
+        _p(last_token), last_token.shape[0], ctx.num_requests, _p(table), _p(pairs), _is_f32(table), _p(out), _p(resolved),
+        tokens, table.shape[1], table.shape[0], ctypes.c_longlong(buckets), ctypes.c_longlong(mul_prev),
+        ctypes.c_longlong(mul_cur), _p(ctx.status), _stream()), "pair_embedding", kernels=2)
+    return out, resolved
+
+
+def token_gate(z: torch.Tensor, ids: torch.Tensor, side: torch.Tensor, offset: int) -> torch.Tensor:
+    """gelu_tanh(z[t, j]) * side[ids[t], offset + j] for z [tokens, dim], in z's type."""
+    z = materialize(z)
+    _contig(z, ids, side)
+    out = torch.empty_like(z)
+    _check(library().vosti_token_gate(_p(z), _is_f32(z), _p(ids), _p(side), _is_f32(side), ctypes.c_int64(side.shape[1]),
+                                      offset, z.shape[1], side.shape[0], _p(out), z.shape[0], _stream()), "token_gate")
+    return out
+
+
 # ---------------------------------------------------------------- attention with bias and sink
 def qkv_store(qkv: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], *, nq: int, nkv: int,
               dk: int, dv: int, page_size: int, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
-              temp_coef: float, temp_every: int, status: torch.Tensor) -> torch.Tensor:
-    """After a q | k | v projection without rotation: the queries times their temperature
+              temp_coef: float, temp_every: int, status: torch.Tensor,
+              freq: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """After a q | k | v projection: the queries times their temperature
     (1 + coef * ln(floor((p + 1) / every) + 1), 1 if coef is 0) are returned [tokens, nq * dk];
-    keys and values go to their cache slots (caches of different widths)."""
+    keys and values go to their cache slots (caches of different widths). With `freq` (float32
+    [n]) the first 2n elements of every query and key head are first turned in pairs (i, i + n) by
+    the angle position * freq[i]."""
     qkv = materialize(qkv)
-    _contig(qkv, k_cache, v_cache, positions, slot_mapping)
+    _contig(qkv, k_cache, v_cache, positions, slot_mapping, freq)
     flag = _same_dtype(qkv, k_cache, v_cache)
     tokens = qkv.shape[0]
+    if freq is not None and freq.dtype != torch.float32:
+        raise KernelError("qkv_store: rotation frequencies are float32")
     if qkv.shape[1] != nq * dk + nkv * (dk + dv):
         raise KernelError("qkv_store: input width does not match the head counts")
     q = torch.empty((tokens, nq * dk), dtype=qkv.dtype, device=qkv.device)
     num_slots = 0 if k_cache is None else k_cache.numel() // (nkv * dk)
     _check(library().vosti_qkv_store(_p(qkv), _p(q), _p(k_cache), _p(v_cache), _p(positions), _p(slot_mapping),
                                      ctypes.c_int64(num_slots), page_size, tokens, nq, nkv, dk, dv,
-                                     ctypes.c_float(temp_coef), int(temp_every), flag, _p(status), _stream()), "qkv_store")
+                                     ctypes.c_float(temp_coef), int(temp_every), flag, _p(status), _p(freq),
+                                     0 if freq is None else freq.shape[0], _stream()), "qkv_store")
     return q
 
 
@@ -767,8 +844,9 @@ def _attention_sink_rows(ctx, q, k_cache, v_cache, out, group, *, token_list, co
 
 def attention_sink(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, *, nq: int, nkv: int,
                    dk: int, dv: int, scale: float, window: int, bias: Optional[torch.Tensor],
-                   sink: Optional[torch.Tensor]) -> torch.Tensor:
-    """Causal attention of every query row over its request's cached keys, with an optional bias
+                   sink: Optional[torch.Tensor], chunk: int = 0) -> torch.Tensor:
+    """Causal attention of every query row over its request's cached keys (the last `window` of
+    them, or with `chunk` those of the query's own chunk of positions), with an optional bias
     table float32 [nq, distances] (base-2 units, the last column serving every larger distance)
     and an optional sink logit per head (float32 [nq], natural units). Returns [tokens, nq * dv].
     bfloat16 with equal key and value widths of 64 or 128 (pages of a multiple of 16 tokens, at
@@ -779,9 +857,12 @@ def attention_sink(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     _contig(q, k_cache, v_cache, bias, sink)
     tokens = q.shape[0]
     out = torch.empty((tokens, nq * dv), dtype=q.dtype, device=q.device)
+    if chunk < 0 or window < 0 or (chunk and window):
+        raise KernelError("attention_sink: a window or a chunk, not both, and neither negative")
+    window = -chunk if chunk else window            # the kernels take a chunk as a negative window
     common = dict(nq=nq, nkv=nkv, dk=dk, dv=dv, scale=scale, window=window, bias=bias, sink=sink)
     lib = library()
-    tensor_memory = (q.dtype == torch.bfloat16 and dk == dv and nq // nkv <= 16
+    tensor_memory = (q.dtype == torch.bfloat16 and dk == dv and nq // nkv <= 16 and not chunk
                      and lib.vosti_attention_prefill_tc_supported(dk, group.page_size))
     if not tensor_memory or getattr(ctx, "layout", None) is None or "attention" not in ctx.layout:
         _attention_sink_rows(ctx, q, k_cache, v_cache, out, group, token_list=None, count=tokens, **common)
@@ -813,7 +894,8 @@ def attention_sink(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
 
 # ---------------------------------------------------------------- gated delta rule
 def delta_prep(proj: torch.Tensor, rates: torch.Tensor, offsets: dict, *, kv_heads: int, heads: int, dk: int, dv: int,
-               taps: int, conv_w, a_log, dt_bias, state: torch.Tensor, conv_offset: int, ctx):
+               taps: int, conv_w, a_log, dt_bias, state: torch.Tensor, conv_offset: int, ctx,
+               decay_per_head: bool = False, gate_silu: bool = False):
     """Everything between the projections and the recurrence (see csrc/delta_rule.cu): `proj` holds
     the columns q | k | v | beta at `offsets`, `rates` [tokens, heads*dk + heads*dv] the low-rank
     pairs' products (decay rates, then output gates, before their activations). Also moves the
@@ -825,7 +907,7 @@ def delta_prep(proj: torch.Tensor, rates: torch.Tensor, offsets: dict, *, kv_hea
     if any(_is_f32(t) != flag for t in small) or state.dtype != torch.float32:
         raise KernelError("delta_prep: the small tensors must share a dtype and the state is float32")
     tokens, dev = proj.shape[0], proj.device
-    if tuple(rates.shape) != (tokens, heads * (dk + dv)):
+    if tuple(rates.shape) != (tokens, (heads if decay_per_head else heads * dk) + heads * dv):
         raise KernelError("delta_prep: the rates do not match the head sizes")
     new = lambda width: torch.empty((tokens, width), dtype=torch.float32, device=dev)
     q, k, v = new(kv_heads * dk), new(kv_heads * dk), new(heads * dv)
@@ -835,7 +917,7 @@ def delta_prep(proj: torch.Tensor, rates: torch.Tensor, offsets: dict, *, kv_hea
         _is_f32(rates), kv_heads, heads, dk, dv, taps, _p(conv_w), _p(a_log), _p(dt_bias), flag, _p(state),
         ctypes.c_int64(state.shape[1]), ctypes.c_int64(conv_offset), _p(ctx.request_of), _p(ctx.cu_q),
         _p(ctx.state_slots), state.shape[0], ctx.num_requests, tokens, _p(q), _p(k), _p(v), _p(beta), _p(decay), _p(gate),
-        _p(ctx.status), _stream()), "delta_prep", kernels=2 if taps > 1 else 1)
+        _p(ctx.status), int(decay_per_head), int(gate_silu), _stream()), "delta_prep", kernels=2 if taps > 1 else 1)
     return q, k, v, beta, decay, gate
 
 
@@ -852,18 +934,61 @@ def delta_scan(q, k, v, beta, decay, state: torch.Tensor, ctx, *, kv_heads: int,
 
 def delta_out(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, *, heads: int, dv: int,
               out_dtype: torch.dtype) -> torch.Tensor:
-    """o / sqrt(mean(o^2) + eps) * weight * gate per (token, head), rounded to `out_dtype`."""
+    """o / sqrt(mean(o^2) + eps) * weight * gate per (token, head), rounded to `out_dtype`; the
+    weight is [dv], shared by the heads, or [heads * dv]."""
     _contig(o, gate, weight)
+    if weight.numel() not in (dv, heads * dv):
+        raise KernelError("delta_out: the weight has one row, or one per head")
     y = torch.empty(o.shape, dtype=out_dtype, device=o.device)
     _check(library().vosti_delta_out(_p(o), _p(gate), _p(weight), _is_f32(weight), _p(y), _is_f32(y), o.shape[0], heads, dv,
-                                     ctypes.c_float(eps), _stream()), "delta_out")
+                                     ctypes.c_float(eps), int(weight.numel() != dv), _stream()), "delta_out")
     return y
 
 
+def tanh_columns(x: torch.Tensor, offset: int, width: int) -> torch.Tensor:
+    """tanh(x[:, offset:offset + width]) as a contiguous tensor of x's type."""
+    x = materialize(x)
+    _contig(x)
+    out = torch.empty((x.shape[0], width), dtype=x.dtype, device=x.device)
+    _check(library().vosti_tanh_columns(_p(x), _is_f32(x), x.shape[1], offset, width, _p(out), x.shape[0], _stream()),
+           "tanh_columns")
+    return out
+
+
+def general_delta_prep(proj: torch.Tensor, inner: torch.Tensor, offsets: dict, *, heads: int, d: int, w0: torch.Tensor,
+                       a_bias: torch.Tensor):
+    """Between the projections and the generalized delta rule's recurrence (csrc/delta_rule.cu):
+    `proj` holds the columns r | k | v | g | a at `offsets`, `inner` float32 [tokens, heads * d] the
+    decay's low-rank product. Returns float32 r, k, v, decay, unit key, removal (rate * unit key), gate."""
+    proj, inner = materialize(proj), materialize(inner)
+    _contig(proj, inner, w0, a_bias)
+    if inner.dtype != torch.float32 or _is_f32(w0) != _is_f32(a_bias) or tuple(inner.shape) != (proj.shape[0], heads * d):
+        raise KernelError("general_delta_prep: the low-rank product is float32 [tokens, heads * d]; the biases share a type")
+    tokens = proj.shape[0]
+    outs = [torch.empty((tokens, heads * d), dtype=torch.float32, device=proj.device) for _ in range(7)]
+    _check(library().vosti_general_delta_prep(
+        _p(proj), _is_f32(proj), proj.shape[1], offsets["r"], offsets["k"], offsets["v"], offsets["g"], offsets["a"],
+        _p(inner), _p(w0), _p(a_bias), _is_f32(w0), heads, d, tokens, *[_p(t) for t in outs], _stream()), "general_delta_prep")
+    return outs
+
+
+def general_delta_scan(r, k, v, decay, unit, removal, state: torch.Tensor, ctx, *, heads: int, d: int) -> torch.Tensor:
+    """The generalized rule's recurrence over every request's tokens of this step, from and to its
+    state slot; returns the read-outs, float32 [tokens, heads * d]."""
+    _contig(r, k, v, decay, unit, removal, state)
+    out = torch.empty((r.shape[0], heads * d), dtype=torch.float32, device=r.device)
+    _check(library().vosti_general_delta_scan(_p(r), _p(k), _p(v), _p(decay), _p(unit), _p(removal), _p(out), _p(state),
+                                              ctypes.c_int64(state.shape[1]), _p(ctx.cu_q), _p(ctx.state_slots),
+                                              state.shape[0], ctx.num_requests, heads, d, d, _stream()), "general_delta_scan")
+    return out
+
+
 # ---------------------------------------------------------------- mixture of experts
-def moe_route(logits: torch.Tensor, top: int):
+def moe_route(logits: torch.Tensor, top: int, *, over_all: bool = False, scale: float = 1.0):
     """The `top` largest of each row of float32 router logits: (expert ids int32 [tokens, top],
-    their softmax weights float32 [tokens, top], the same weights as a dense [tokens, experts])."""
+    their weights float32 [tokens, top], the same weights as a dense [tokens, experts]). The
+    weights are the softmax over the chosen logits, or with `over_all` the chosen experts' shares
+    of a softmax over all experts divided by their sum (+ 1e-20); both times `scale`."""
     if logits.dtype != torch.float32:
         raise KernelError("moe_route: router logits are float32")
     _contig(logits)
@@ -871,15 +996,17 @@ def moe_route(logits: torch.Tensor, top: int):
     chosen = torch.empty((tokens, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((tokens, top), dtype=torch.float32, device=logits.device)
     dense = torch.empty((tokens, experts), dtype=torch.float32, device=logits.device)
-    _check(library().vosti_moe_route(_p(logits), tokens, experts, top, _p(chosen), _p(weights), _p(dense), _stream()),
-           "moe_route")
+    _check(library().vosti_moe_route(_p(logits), tokens, experts, top, _p(chosen), _p(weights), _p(dense), int(over_all),
+                                     ctypes.c_float(scale), _stream()), "moe_route")
     return chosen, weights, dense
 
 
-def moe_scale(act: torch.Tensor, dense: torch.Tensor, ff: int) -> torch.Tensor:
-    """act[t, e * ff + i] *= dense[t, e], in place."""
+def moe_scale(act: torch.Tensor, dense: Optional[torch.Tensor], ff: int, *, gelu: bool = False) -> torch.Tensor:
+    """act[t, e * ff + i] <- f(act[t, e * ff + i]) * dense[t, e], in place; f is the exact GELU with
+    `gelu`, else the identity; without `dense` the activation alone."""
     _contig(act, dense)
-    _check(library().vosti_moe_scale(_p(act), _p(dense), act.shape[0], dense.shape[1], ff, _is_f32(act), _stream()),
+    experts = dense.shape[1] if dense is not None else act.shape[1] // ff
+    _check(library().vosti_moe_scale(_p(act), _p(dense), act.shape[0], experts, ff, _is_f32(act), int(gelu), _stream()),
            "moe_scale")
     return act
 

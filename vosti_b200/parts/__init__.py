@@ -1,17 +1,19 @@
-from .base import (Embedding, FeedForward, Head, Mixer, Norm, PagedCacheSpec, Part, PositionEncoding, StateSpec,
-                   build_embedding, build_feed_forward, build_head, build_mixer, build_norm, build_position, build_reentry,
+from .base import (Embedding, FeedForward, Head, Mixer, Norm, PagedCacheSpec, Part, PositionEncoding, StateSpec, TokenInput,
+                   build_embedding, build_feed_forward, build_head, build_mixer, build_norm, build_position, build_reentry, build_token_input,
                    part_factory, register_part, register_step_layout, unregister_part)
 from .linear import linear, prepare_weight
-from .norm import DynamicTanh, RMSNorm
+from .norm import DynamicTanh, RMSNorm, StreamRMSNorm
 from .rope import RotaryEncoding
 from .attention import Attention
 from .feed_forward import ExpertMixture, SwiGLU
 from .sink_attention import SinkAttention
 from .gated_delta import GatedDeltaRule
+from .general_delta import GeneralDeltaRule
+from .token_input import GatedTokenInput
 from .branches import BranchMixer
 from .reentry import ConcatReentry
-from .block import ParallelBlock, PreNormBlock, build_block
-from .embedding import TableEmbedding
+from .block import ParallelBlock, PreNormBlock, StreamPreNormBlock, build_block
+from .embedding import PairHashEmbedding, TableEmbedding
 from .head import LinearHead
 
 __all__ = [
@@ -19,5 +21,6 @@ __all__ = [
     "build_feed_forward", "build_mixer", "build_norm", "build_position", "part_factory",
     "register_part", "register_step_layout", "unregister_part", "linear", "RMSNorm", "RotaryEncoding", "Attention",
     "SwiGLU", "PreNormBlock", "build_block", "build_reentry", "DynamicTanh", "ExpertMixture", "SinkAttention",
-    "GatedDeltaRule", "BranchMixer", "ConcatReentry", "ParallelBlock",
+    "GatedDeltaRule", "BranchMixer", "ConcatReentry", "ParallelBlock", "StreamRMSNorm", "GeneralDeltaRule",
+    "GatedTokenInput", "StreamPreNormBlock", "PairHashEmbedding", "TokenInput", "build_token_input",
 ]

@@ -11,6 +11,7 @@ them in `load`, and computes in `forward`. No part knows which model it is in.
                    of fixed size (`state_spec`).
 * FeedForward:     forward(ctx, x) -> y
 * Arrangement:     how a block wires mixer, feed-forward and norms around the residual.
+* TokenInput:      forward(ctx, x) -> y, a sublayer that reads the step's token ids again
 * Embedding:       forward(ctx, tokens, feedback) -> hidden rows; `table()` for a tied head
 * Head:            forward(ctx, x) -> float32 logits
 
@@ -126,8 +127,19 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class TokenInput(Part):
+    """A sublayer fed by the stream and by the token ids of the step: it finds the ids (with those
+    a sampler left on the device filled in) in `ctx.extras["token_ids"]` and whatever table of
+    per-token vectors the model's embedding part publishes in `ctx.extras["token_table"]`."""
+
+    def forward(self, ctx, x):
+        raise NotImplementedError
+
+
 class Embedding(Part):
-    """Token ids to rows of the hidden width. `feedback` = (source, values) names tokens to take
+    """Token ids to rows of the hidden width. An embedding that keeps something per request (the
+    token before a portion's first one) declares it with `state_spec()`; the model then hands
+    `forward` the cache that holds it (`cache.state[slot]`). `feedback` = (source, values) names tokens to take
     from a device array instead (see ops.embedding)."""
 
     def __init__(self, spec: PartSpec, hidden_size: int, vocab_size: int):
@@ -140,6 +152,9 @@ class Embedding(Part):
     def table(self) -> Optional[torch.Tensor]:
         """The [vocab, hidden] tensor a tied output head multiplies with, or None if this
         embedding has no such table."""
+        return None
+
+    def state_spec(self) -> Optional[StateSpec]:
         return None
 
 
@@ -160,7 +175,7 @@ class Head(Part):
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {
     "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "arrangement": {}, "embedding": {}, "head": {},
-    "reentry": {},
+    "reentry": {}, "token_input": {},
 }
 
 
@@ -182,7 +197,7 @@ def step_layout_providers() -> Dict[str, Callable]:
 
 def register_part(role: str, kind: str, factory: Callable, *, replace: bool = False) -> None:
     """Register `factory` for parts of `role` ('norm', 'position', 'mixer', 'feed_forward',
-    'arrangement', 'embedding', 'head', 'reentry') with the given kind."""
+    'arrangement', 'embedding', 'head', 'reentry', 'token_input') with the given kind."""
     if role not in _REGISTRIES:
         raise ConfigError(f"unknown part role '{role}'; roles: {sorted(_REGISTRIES)}")
     if kind in _REGISTRIES[role] and not replace:
@@ -231,6 +246,12 @@ def build_reentry(spec: Optional[PartSpec], hidden_size: int) -> Optional[Part]:
     if spec is None:
         return None
     return part_factory("reentry", spec.kind)(spec, hidden_size)
+
+
+def build_token_input(spec: Optional[PartSpec], hidden_size: int) -> Optional[TokenInput]:
+    if spec is None:
+        return None
+    return part_factory("token_input", spec.kind)(spec, hidden_size)
 
 
 def build_feed_forward(spec: Optional[PartSpec], hidden_size: int) -> Optional[FeedForward]:

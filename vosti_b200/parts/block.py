@@ -10,10 +10,12 @@ from __future__ import annotations
 
 from typing import Dict
 
+import torch
+
 from .. import ops
 from ..config.schema import ConfigError, LayerSpec
 from ..weights.loader import WeightSpec
-from .base import build_feed_forward, build_mixer, build_norm, part_factory, register_part
+from .base import Norm, build_feed_forward, build_mixer, build_norm, build_token_input, part_factory, register_part
 
 
 class PreNormBlock:
@@ -138,3 +140,80 @@ class ParallelBlock:
 
 
 register_part("arrangement", "parallel", ParallelBlock, replace=True)
+
+
+class StreamPreNormBlock:
+    """'pre_norm_stream': the pre-norm wiring over a float32 residual stream,
+
+        x <- x + mixer(norm1(x));   x <- x + ff(norm2(x));   x <- x + token_input(x)
+
+    with norms that keep the stream (`StreamRMSNorm`, `DynamicTanh`); the feed-forward and the token
+    input (`LayerSpec.token_input`, a part of role "token_input" that reads the stream itself, not
+    a normed copy) are optional. Adds are deferred like the other blocks': a block receives the
+    stream and what the block before left to be added, its first norm adds while it reads, and
+    it returns its last sublayer's output unadded.
+
+    Checkpoint names: `LayerSpec.names` maps the roles "input_norm", "post_norm", "mixer",
+    "feed_forward", "token_input" to name fragments; a norm's `weight` tensor is called by the
+    fragment itself, every other tensor `<fragment>.<key>`."""
+
+    def __init__(self, spec: LayerSpec, hidden_size: int):
+        self.spec = spec
+        if spec.position is not None:
+            raise ConfigError("pre_norm_stream block: position encodings belong to the mixers that apply them")
+        self.mixer = build_mixer(spec.mixer, hidden_size, None)
+        self.feed_forward = build_feed_forward(spec.feed_forward, hidden_size)
+        self.input_norm = build_norm(spec.norm, hidden_size)
+        self.post_norm = build_norm(spec.norm, hidden_size) if self.feed_forward is not None else None
+        self.token_input = build_token_input(spec.token_input, hidden_size)
+        self.capture_safe = True
+
+    def _children(self):
+        n = self.spec.name_of
+        yield n("input_norm"), self.input_norm
+        yield n("mixer"), self.mixer
+        if self.feed_forward is not None:
+            yield n("post_norm"), self.post_norm
+            yield n("feed_forward"), self.feed_forward
+        if self.token_input is not None:
+            yield n("token_input"), self.token_input
+
+    def _names(self):
+        """(checkpoint name relative to the layer, part, the part's key) for every tensor."""
+        for fragment, part in self._children():
+            for key in part.weight_specs():
+                bare = isinstance(part, Norm) and key == "weight"
+                yield (fragment if bare else f"{fragment}.{key}"), part, key
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {name: part.weight_specs()[key] for name, part, key in self._names()}
+
+    def load(self, tensors, dtype):
+        per_part = {}
+        for name, part, key in self._names():
+            if name in tensors:
+                per_part.setdefault(id(part), (part, {}))[1][key] = tensors[name]
+        for part, own in per_part.values():
+            part.load(own, dtype)
+
+    def setup(self, device, dtype):
+        for _, part in self._children():
+            part.setup(device, dtype)
+
+    def forward(self, ctx, hidden, residual, cache, writes_cache=True):
+        if residual is None and isinstance(hidden, torch.Tensor) and hidden.dtype == torch.float32:
+            residual, normed = hidden, self.input_norm.forward(ctx, hidden)      # float32 embedding rows are the stream
+        else:
+            normed, residual = self.input_norm.forward_add(ctx, hidden, residual)
+        out = self.mixer.forward(ctx, normed, cache, writes_cache)
+        if self.feed_forward is not None:
+            normed, residual = self.post_norm.forward_add(ctx, out, residual)
+            out = self.feed_forward.forward(ctx, normed)
+        if self.token_input is not None:
+            # this sublayer reads the stream itself: the pending output is added now
+            x = ops.rms_stream(out, None, 0.0, ctx.dtype, stream=residual, stream_out=residual)
+            out = self.token_input.forward(ctx, x)
+        return ops.DeferredSum(out), residual
+
+
+register_part("arrangement", "pre_norm_stream", StreamPreNormBlock, replace=True)

@@ -11,6 +11,9 @@ float32: the down projection is then not rounded to the serving type.
 
 `ExpertMixture` is the same feed-forward as `experts` small ones, of which each token uses
 the `top` with the largest router logits, weighted by the softmax over the chosen logits only.
+Its experts may also be plain two-matrix feed-forwards, down(gelu(up(x))) with the exact (erf)
+GELU, and its weights the chosen experts' shares of a softmax over all experts, divided by
+their sum and multiplied by a constant.
 """
 from __future__ import annotations
 
@@ -83,7 +86,11 @@ register_part("feed_forward", "swiglu", SwiGLU, replace=True)
 
 class ExpertMixture(FeedForward):
     """Parameters: experts, top, intermediate_size (of one expert), `float32_out`. Tensors:
-    `router` [experts, hidden] and `e<i>.gate`, `e<i>.up`, `e<i>.down`.
+    `router` [experts, hidden] and `e<i>.gate`, `e<i>.up`, `e<i>.down`. Further parameters:
+    `gated` (default true; false: experts are down(gelu(up(x))), no `gate` tensors), `route`
+    ("top_softmax", the default: softmax over the chosen logits; "softmax_renorm": softmax over
+    all experts, the chosen scores divided by their sum + 1e-20) and `scale`, a constant on the
+    weights (default 1).
 
     The router's logits are float32. The experts' gate and up matrices stand side by side as one
     [2 * experts * I, hidden] matrix and their down matrices as one [hidden, experts * I]: every
@@ -106,8 +113,12 @@ class ExpertMixture(FeedForward):
         self.experts, self.top = int(spec["experts"]), int(spec["top"])
         self.inter = int(spec["intermediate_size"])
         self.float32_out = bool(spec.get("float32_out", False))
+        self.gated = bool(spec.get("gated", True))
+        self.route, self.scale = spec.get("route", "top_softmax"), float(spec.get("scale", 1.0))
         if self.experts <= 0 or not 0 < self.top <= self.experts or self.inter <= 0:
             raise ConfigError("moe: experts, top (at most experts) and intermediate_size must be positive")
+        if self.route not in ("top_softmax", "softmax_renorm") or self.scale != self.scale:
+            raise ConfigError("moe: route is 'top_softmax' or 'softmax_renorm' and scale a number")
         self.router = self.w_gate_up = self.w_down = None
         self.fused = False
 
@@ -115,23 +126,38 @@ class ExpertMixture(FeedForward):
         h, i = self.hidden_size, self.inter
         specs = {"router": WeightSpec((self.experts, h), std=0.5)}
         for e in range(self.experts):
-            specs.update({f"e{e}.gate": WeightSpec((i, h)), f"e{e}.up": WeightSpec((i, h)), f"e{e}.down": WeightSpec((h, i))})
+            specs.update({f"e{e}.up": WeightSpec((i, h)), f"e{e}.down": WeightSpec((h, i))})
+            if self.gated:
+                specs[f"e{e}.gate"] = WeightSpec((i, h))
         return specs
 
     def load(self, tensors, dtype):
         self.router = tensors["router"].float().contiguous()        # 32-bit logits from exact 32-bit products
-        gate = torch.cat([tensors[f"e{e}.gate"] for e in range(self.experts)], dim=0)
         up = torch.cat([tensors[f"e{e}.up"] for e in range(self.experts)], dim=0)
-        self.w_gate_up, self.fused = stack_gate_up(gate, up, dtype)
+        if self.gated:
+            gate = torch.cat([tensors[f"e{e}.gate"] for e in range(self.experts)], dim=0)
+            self.w_gate_up, self.fused = stack_gate_up(gate, up, dtype)
+        else:
+            self.w_gate_up, self.fused = prepare_weight(up.contiguous(), dtype), False
         self.w_down = prepare_weight(torch.cat([tensors[f"e{e}.down"] for e in range(self.experts)], dim=1).contiguous(), dtype)
         self.per_expert = []
         if self.top < self.experts:
             for e in range(self.experts):
-                gate_up, fused = stack_gate_up(tensors[f"e{e}.gate"], tensors[f"e{e}.up"], dtype)
+                if self.gated:
+                    gate_up, fused = stack_gate_up(tensors[f"e{e}.gate"], tensors[f"e{e}.up"], dtype)
+                else:
+                    gate_up, fused = prepare_weight(tensors[f"e{e}.up"], dtype), False
                 self.per_expert.append((gate_up, fused, prepare_weight(tensors[f"e{e}.down"], dtype)))
 
     def first_weight(self):
         return self.w_gate_up
+
+    def _activation(self, ctx, x, w_first, fused, dense=None):
+        """An expert's (or all experts') hidden activation, times the dense weights if given."""
+        if self.gated:
+            act = gated_activation(ctx, x, w_first, fused)
+            return act if dense is None else ops.moe_scale(act, dense, self.inter)
+        return ops.moe_scale(ops.materialize(linear(ctx, x, w_first)), dense, self.inter, gelu=True)
 
     def _grouped(self, ctx, x, chosen, weights):
         offsets, rows, where = ops.moe_group(chosen, self.experts)
@@ -141,19 +167,19 @@ class ExpertMixture(FeedForward):
         for e, (gate_up, fused, down) in enumerate(self.per_expert):
             lo, hi = bounds[e], bounds[e + 1]
             if hi > lo:
-                act = gated_activation(ctx, gathered[lo:hi], gate_up, fused)
+                act = self._activation(ctx, gathered[lo:hi], gate_up, fused)
                 y[lo:hi].copy_(linear(ctx, act, down, out_dtype=torch.float32))
         return ops.moe_combine(y, where, weights)
 
     def forward(self, ctx, x):
         x = ops.materialize(x)
         logits = ops.gemm_simt(x, self.router, ctx.status, out_dtype=torch.float32)
-        chosen, weights, dense = ops.moe_route(logits, self.top)
+        chosen, weights, dense = ops.moe_route(logits, self.top, over_all=self.route == "softmax_renorm", scale=self.scale)
         if (self.per_expert and x.shape[0] >= self.GROUPED_FROM and not getattr(ctx, "all_decode", True)
                 and not torch.cuda.is_current_stream_capturing()):
             out = self._grouped(ctx, x, chosen, weights)
             return out if self.float32_out else out.to(x.dtype)
-        act = ops.moe_scale(gated_activation(ctx, x, self.w_gate_up, self.fused), dense, self.inter)
+        act = self._activation(ctx, x, self.w_gate_up, self.fused, dense)
         if self.float32_out:
             return linear(ctx, act, self.w_down, out_dtype=torch.float32)
         return linear(ctx, act, self.w_down, allow_partial=True)

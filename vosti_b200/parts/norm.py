@@ -82,3 +82,44 @@ class DynamicTanh(Norm):
 
 
 register_part("norm", "dyt", DynamicTanh, replace=True)
+
+
+class StreamRMSNorm(Norm):
+    """Root-mean-square norm for models whose residual stream is float32 in both serving types:
+    x / sqrt(mean(x^2) + eps) * (offset + weight), in float32, rounded to the serving type.
+    Parameters: `eps`; `unit_offset` (default false): the weight is stored around zero and one is
+    added to it. `forward_add` takes the stream and what is still to be added to it (a tensor or
+    an `ops.DeferredSum`), adds in float32, stores the sum as the new stream and norms it.
+    `out_dtype` "float32" keeps the normed rows unrounded (for a sublayer's output that is itself
+    added to the stream)."""
+
+    def __init__(self, spec: PartSpec, width: int):
+        super().__init__(spec, width)
+        self.eps = float(spec["eps"])
+        self.offset = 1.0 if bool(spec.get("unit_offset", False)) else 0.0
+        self.float32_out = spec.get("out_dtype") == "float32"
+        self.width = width
+        self.weight = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {"weight": WeightSpec((self.width,), init="linear" if self.offset else "norm", std=0.1)}
+
+    def load(self, tensors, dtype):
+        self.weight = tensors["weight"]
+
+    def _out(self, ctx):
+        return torch.float32 if self.float32_out else ctx.dtype
+
+    def forward(self, ctx, x):
+        return ops.rms_stream(x, self.weight, self.eps, self._out(ctx), offset=self.offset)
+
+    def forward_add(self, ctx, x, residual):
+        if residual is None:
+            first = ops.materialize(x.terms[0] if isinstance(x, ops.DeferredSum) else x)
+            residual = torch.empty(first.shape, dtype=torch.float32, device=first.device)
+            return ops.rms_stream(x, self.weight, self.eps, self._out(ctx), offset=self.offset, stream_out=residual), residual
+        return ops.rms_stream(x, self.weight, self.eps, self._out(ctx), offset=self.offset, stream=residual,
+                              stream_out=residual), residual
+
+
+register_part("norm", "rms_stream", StreamRMSNorm, replace=True)

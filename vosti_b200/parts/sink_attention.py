@@ -1,6 +1,13 @@
-"""Grouped-query attention without rotation whose key and value heads may differ in width,
-with three additions, each of them optional and a parameter of the spec:
+"""Grouped-query attention whose key and value heads may differ in width, with additions, each
+of them optional and a parameter of the spec:
 
+* `position`: the `PartSpec` of a rotation (kind "rope"); the first `rotary_dim` elements of every
+  query and key head turn in pairs (i, i + rotary_dim / 2) by position * frequency, the angle
+  formed in float32 in the kernel (no table, no limit on positions);
+* `chunk`: instead of a `window`, a query sees only the earlier keys that lie in the same block of
+  `chunk` consecutive absolute positions as itself (blocks start at multiples of `chunk`);
+* `sink_value`: a constant logit that joins the softmax denominator (0.0: one is added to the sum
+  of exponentials), where `sink` is a learned one per head;
 * `q_temp_coef`, `q_temp_every`: the query at position p is multiplied by
   1 + coef * ln(floor((p + 1) / every) + 1) (long contexts sharpen their scores);
 * `bias_rows`, `bias_far`: a learned table `rel` [rows, heads] is added to the scaled score
@@ -23,7 +30,7 @@ import torch
 from .. import ops
 from ..config.schema import ConfigError, PartSpec
 from ..weights.loader import WeightSpec
-from .base import Mixer, PagedCacheSpec, PositionEncoding, register_part
+from .base import Mixer, PagedCacheSpec, PositionEncoding, build_position, register_part
 from .linear import linear, prepare_weight
 
 LOG2E = 1.4426950408889634
@@ -40,7 +47,7 @@ class SinkAttention(Mixer):
     def __init__(self, spec: PartSpec, hidden_size: int, position: Optional[PositionEncoding]):
         super().__init__(spec, hidden_size, position)
         if position is not None:
-            raise ConfigError("sink_attention: this mixer applies no position encoding to q and k")
+            raise ConfigError("sink_attention: the rotation is named by the mixer's own `position` parameter")
         self.nq, self.nkv = int(spec["num_heads"]), int(spec["num_kv_heads"])
         self.dk, self.dv = int(spec["head_dim"]), int(spec.get("v_head_dim") or spec["head_dim"])
         self.scale = float(spec["scale"])
@@ -50,6 +57,16 @@ class SinkAttention(Mixer):
         self.bias_rows = int(spec.get("bias_rows", 0) or 0)
         self.bias_far = int(spec.get("bias_far", 0) or 0)
         self.has_sink = bool(spec.get("sink", False))
+        self.sink_value = spec.get("sink_value")
+        self.chunk = int(spec.get("chunk", 0) or 0)
+        self.rotation = build_position(spec.get("position"), hidden_size, self.dk)
+        self.freq = None
+        if self.has_sink and self.sink_value is not None:
+            raise ConfigError("sink_attention: a learned sink or a constant one, not both")
+        if self.chunk < 0 or (self.chunk and self.window):
+            raise ConfigError("sink_attention: a window or a chunk, not both, and neither negative")
+        if self.rotation is not None and (not hasattr(self.rotation, "frequencies") or self.rotation.interleaved):
+            raise ConfigError("sink_attention: the rotation must give frequencies and pair element i with i + rotary_dim / 2")
         if self.nq <= 0 or self.nkv <= 0 or self.nq % self.nkv:
             raise ConfigError(f"sink_attention: num_heads {self.nq} must be a positive multiple of num_kv_heads {self.nkv}")
         if not 0 < self.dk <= 256 or not 0 < self.dv <= 256:
@@ -88,6 +105,12 @@ class SinkAttention(Mixer):
             index = torch.tensor(rows, dtype=torch.long, device=rel.device)
             self.bias_table = (rel[index].T * LOG2E).contiguous()
 
+    def setup(self, device, dtype):
+        if self.rotation is not None:
+            self.freq = self.rotation.frequencies().to(device=device, dtype=torch.float32).contiguous()
+        if self.sink_value is not None:
+            self.sink = torch.full((self.nq,), float(self.sink_value), dtype=torch.float32, device=device)
+
     def first_weight(self):
         return self.w_qkv
 
@@ -100,9 +123,9 @@ class SinkAttention(Mixer):
         q = ops.qkv_store(qkv, cache.k if writes_cache else None, cache.v if writes_cache else None, nq=self.nq,
                           nkv=self.nkv, dk=self.dk, dv=self.dv, page_size=group.page_size, positions=ctx.positions,
                           slot_mapping=group.slot_mapping, temp_coef=self.temp_coef, temp_every=self.temp_every,
-                          status=ctx.status)
+                          status=ctx.status, freq=self.freq)
         attn = ops.attention_sink(ctx, q, cache.k, cache.v, group, nq=self.nq, nkv=self.nkv, dk=self.dk, dv=self.dv,
-                                  scale=self.scale, window=self.window, bias=self.bias_table, sink=self.sink)
+                                  scale=self.scale, window=self.window, bias=self.bias_table, sink=self.sink, chunk=self.chunk)
         return linear(ctx, attn, self.w_o, out_dtype=torch.float32)
 
 
