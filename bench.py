@@ -28,6 +28,11 @@ Mugizen design (parallel blocks of sink attention beside a gated delta rule over
 stream) at layer sizes that resemble a real model's (`--design-sizes s,m,moe`), beside Qwen3 at
 the same width, heads, feed-forward width, layer count and vocabulary: one 2,048-token prefill
 and decode steps at batch 8 and 1 for each, with their shares of the measured peaks.
+
+`--design vivesun` does the same for the Vivesun design (pre-norm layers over a float32 stream,
+gated-delta layers alternating with layers of chunked rotary attention beside a generalized
+delta rule, an expert feed-forward in every layer) beside Mugizen, the engine's closest
+model, at the same sizes.
 """
 from __future__ import annotations
 
@@ -370,8 +375,43 @@ def mugizen_config(size):
     return config, checkpoint_shapes(config, bias_rows=32, decay_rank=64, gate_rank=64)
 
 
+def vivesun_config(size):
+    """A Vivesun config.json of these sizes: gated-delta layers and parallel layers in turn, every
+    layer with an expert feed-forward (two of eight experts; where the size names a dense
+    feed-forward the experts are 3/4 of its width, so that a token's two two-matrix experts do
+    the work of one three-matrix feed-forward), and the shape that gives the decay pair's rank."""
+    from vosti_b200.config.vivesun import checkpoint_shapes
+    moe = size["moe"] or dict(experts=8, top=2, ff=size["ff"] * 3 // 4)
+    mlp = dict(kind="moe", expert=dict(ff=moe["ff"]), router=dict(experts=moe["experts"], top=moe["top"], scale=1.0))
+    left = dict(heads=size["heads"], kv_heads=size["kv"], dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=1024),
+                rot=dict(base=500000.0, dims=64, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
+    parallel = dict(type="parallel", mlp=mlp, mixer=dict(left=left, right=dict(heads=size["heads"], dim=128),
+                                                         left_scale=0.8, right_scale=0.9))
+    delta = dict(type="delta", mlp=mlp, mixer=dict(heads=size["heads"], kv_heads=size["kv"], dim=128, vdim=128, conv=4))
+    config = dict(architecture="Vivesun", vocab=size["vocab"], width=size["width"], norm=dict(eps=1e-6), token_side=dict(dim=64),
+                  embedding=dict(bigram=dict(buckets=65521, mul_prev=127, mul_cur=7)),
+                  layers=[delta if i % 2 == 0 else parallel for i in range(size["layers"])])
+    return config, checkpoint_shapes(config, decay_rank=64)
+
+
+def vivesun_flops(size, tokens):
+    """Multiply-add work of one prompt, times two, for `vivesun_config(size)`."""
+    W, H, G, L, V, d = size["width"], size["heads"], size["kv"], size["layers"], size["vocab"], 128
+    moe = size["moe"] or dict(experts=8, top=2, ff=size["ff"] * 3 // 4)
+    feed = 2 * W * moe["ff"] * moe["top"] + W * moe["experts"] + 2 * W * 64            # experts, router, token input
+    delta = W * (2 * G * d + H * d + H) + W * (H + H * d) + H * d * W                  # q | k | v | beta, a | g, o
+    parallel = W * (H + 2 * G) * d + H * d * W + W * (5 * H * d + 64) + 64 * H * d + H * d * W
+    per_token = (L - L // 2) * (delta + feed) + (L // 2) * (parallel + feed)
+    chunk = min(tokens, 1024)
+    scores = (L // 2) * H * d * 4.0 * tokens * (chunk + 1) / 2                          # a query sees at most its chunk
+    state = L * tokens * H * 4.0 * d * d                                               # 4 passes over a 128 x 128 state
+    return 2.0 * tokens * per_token + 2.0 * V * W + scores + state
+
+
 def design_flops(size, tokens, design):
     """Multiply-add work of one prompt of `tokens` tokens, times two: the products and the attention."""
+    if design == "vivesun":
+        return vivesun_flops(size, tokens)
     W, H, G, F, L, V = size["width"], size["heads"], size["kv"], size["ff"], size["layers"], size["vocab"]
     d = 128
     attention = W * (H + 2 * G) * d + H * d * W
@@ -395,6 +435,9 @@ def design_engine(kind, size, max_batch):
 
     if kind == "mugizen":
         config, shapes = mugizen_config(size)
+        spec = model_spec_from_config(config, shapes)
+    elif kind == "vivesun":
+        config, shapes = vivesun_config(size)
         spec = model_spec_from_config(config, shapes)
     else:
         spec = model_spec_from_config(qwen3(size["layers"], size["width"], size["heads"], size["kv"], size["ff"],
@@ -441,7 +484,8 @@ def design_one(args, name, kind) -> dict:
 
 
 def design_main(args) -> int:
-    """Prefill and decode of the Mugizen design beside Qwen3 at equal sizes; one JSON line. Every
+    """Prefill and decode of a design beside the engine's closest other model (Mugizen beside Qwen3,
+    Vivesun beside Mugizen) at equal sizes; one JSON line. Every
     model is measured in a process of its own (this program started again with --design-one), so
     that no model's scratch buffers, graphs or allocator state reach the next one's timings."""
     if args.design_one:
@@ -453,7 +497,7 @@ def design_main(args) -> int:
     for name in args.design_sizes.split(","):
         size = DESIGN_SIZES[name]
         row = {}
-        for kind in ("mugizen", "qwen3"):
+        for kind in (args.design, "mugizen" if args.design == "vivesun" else "qwen3"):
             if kind == "qwen3" and size["moe"]:
                 continue                      # the engine has no other model with experts to stand beside
             child = subprocess.run([sys.executable, os.path.abspath(__file__), "--design", args.design, "--design-one",
@@ -465,7 +509,7 @@ def design_main(args) -> int:
                 raise RuntimeError(f"measuring {kind} at size {name} failed (exit code {child.returncode})")
             row[kind] = json.loads(lines[-1])
         out[name] = {"sizes": {k: v for k, v in size.items()}, **row}
-    print(json.dumps({"design": "mugizen", "beside": "qwen3 at equal sizes", "context": CONTEXT, "page_size": PAGE,
+    print(json.dumps({"design": args.design, "beside": ("mugizen" if args.design == "vivesun" else "qwen3") + " at equal sizes", "context": CONTEXT, "page_size": PAGE,
                       "steps": args.steps, "warmup": args.warmup, "dtype": "bf16", "peaks": peak_kind,
                       "data": "synthetic: random token ids, random-init weights", "results": out}))
     return 0
@@ -493,7 +537,7 @@ def main() -> int:
                         help="read every step's tokens before the next step is planned (default: the engine's async scheduling)")
     parser.add_argument("--batch-invariant", default="off", choices=["off", "decode", "full"],
                         help="measure with the engine's bitwise-invariance modes (the default run has them off)")
-    parser.add_argument("--design", default="", choices=["", "mugizen"],
+    parser.add_argument("--design", default="", choices=["", "mugizen", "vivesun"],
                         help="measure this design beside Qwen3 at equal layer sizes instead of the headline")
     parser.add_argument("--design-sizes", default="s,m,moe", help="which of the sizes s, m, moe (comma-separated)")
     parser.add_argument("--design-one", default="", help=argparse.SUPPRESS)      # size:design, one model in this process

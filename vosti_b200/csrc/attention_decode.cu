@@ -134,7 +134,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         const int pos = __shfl_sync(0xffffffffu, pos_l, j), req = __shfl_sync(0xffffffffu, req_l, j);
         const int idx = (int)blockIdx.x + (base + j) * (int)gridDim.x;
         const int seg = idx / pairs;
-        const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        const int kstart = first_visible_key(pos, window);
         const int seg_begin = seg * segment_keys;
         const int first_index = seg_begin / page_size;
         const int lo = kstart / page_size, hi = min(pos, seg_begin + segment_keys - 1) / page_size;
@@ -153,7 +153,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         const int seg = idx / pairs;
         const int g = (idx % pairs) % nkv;
         const int item = (idx % pairs) / nkv;
-        const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        const int kstart = first_visible_key(pos, window);
         const int seg_begin = seg * segment_keys, seg_end = min(seg_begin + segment_keys, pos + 1);
         if (whole_pages) {
           __syncwarp();
@@ -704,7 +704,7 @@ int launch_decode(const void* q, const void* k_cache, const void* v_cache, void*
   VOSTI_REQUIRE(count >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention_decode: bad head counts nq=%d nkv=%d", nq, nkv);
   VOSTI_REQUIRE(nq / nkv <= 16, "attention_decode: at most 16 query heads per kv head, got %d", nq / nkv);
   VOSTI_REQUIRE(d > 0 && d % 16 == 0 && d <= 256, "attention_decode: head_dim %d must be a multiple of 16 and <= 256", d);
-  VOSTI_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0 && window >= 0, "attention_decode: bad cache geometry");
+  VOSTI_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0, "attention_decode: bad cache geometry");
   VOSTI_REQUIRE(max_kv_len > 0, "attention_decode: max_kv_len %d must be positive", max_kv_len);
   if (count == 0) return VOSTI_OK;
   const int group = nq / nkv;

@@ -157,7 +157,7 @@ attention_decode_once_kernel(const __grid_constant__ CUtensorMap map_k, const __
   cluster_arrive_all();
   pdl_launch_dependents();
 
-  const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int kstart = first_visible_key(pos, window);
   const int seg_begin = seg * segment_keys, seg_end = min(seg_begin + segment_keys, pos + 1);
   const bool visible = !(seg_begin > pos || seg_end <= kstart);
   const int p_first = kstart / segment_keys, p_last = min(pos / segment_keys, segments - 1);   // the segments that hold visible keys

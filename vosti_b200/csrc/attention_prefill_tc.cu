@@ -100,7 +100,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   // keys a row tile sees: [its first row's window start, its last row's position]; the CTA walks
   // the tiles from the first tile's first key to the last tile's last key, a row tile stops at
   // its own end
-  const int first_key = (window > 0 && shift + token0 - window + 1 > 0) ? shift + token0 - window + 1 : 0;
+  const int first_key = first_visible_key(shift + token0, window);
   const int tile_begin = (first_key / KT) * KT;
   int tiles_of[ROW_TILES], key_end = 0;
 #pragma unroll
@@ -145,7 +145,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int token = token0 + wg * tokens_per_tile + r / group;
     const bool valid = r < rows_used && token < q_len;
     const int pos = valid ? shift + token : -1;                  // -1: no key is visible, nothing is written
-    const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int kstart = first_visible_key(pos, window);
     const int my_tiles = wg ? tiles_of[1] : tiles_of[0];
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     // m_run is the maximum the exponentials are taken against. It follows the true running
@@ -448,7 +448,7 @@ int launch_prefill_tc(const void* q, const void* k_cache, const void* v_cache, v
   VOSTI_REQUIRE(nq / nkv <= 16, "attention_prefill_tc: at most 16 query heads per kv head, got %d", nq / nkv);
   VOSTI_REQUIRE(vosti_attention_prefill_tc_supported(d, page_size),
                 "attention_prefill_tc: head_dim %d must be 64 or 128 and page_size %d a multiple of 16", d, page_size);
-  VOSTI_REQUIRE(max_pages > 0 && num_pages > 0 && window >= 0 && tokens_total > 0, "attention_prefill_tc: bad geometry");
+  VOSTI_REQUIRE(max_pages > 0 && num_pages > 0 && tokens_total > 0, "attention_prefill_tc: bad geometry");
   VOSTI_REQUIRE(scale > 0.f, "attention_prefill_tc: the score scale must be positive");
   VOSTI_REQUIRE(count <= 65535, "attention_prefill_tc: too many requests for one launch");
   if (count == 0 || max_q_len <= 0) return VOSTI_OK;

@@ -95,22 +95,40 @@ qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict
     return x;
   };
   // bfloat16 rows whose widths allow it move as 16-byte words (8 elements)
-  const bool vec = rot_half == 0 && sizeof(T) == 2 && dk % 8 == 0 && dv % 8 == 0;
+  // (a rotated half must then be whole words too, so that a word's partner is a word)
+  const bool vec = rot_half % 8 == 0 && sizeof(T) == 2 && dk % 8 == 0 && dv % 8 == 0;
+  // word i (8 elements) of a row of heads of width dk, turned if it lies in the rotated part, times `by`
+  auto turned_word = [&](const uint4* src, int i, float by) {
+    uint4 raw = src[i];
+    const int j = (i * 8) % dk;
+    if (j >= 2 * rot_half && by == 1.f) return raw;
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&raw);
+    if (j < 2 * rot_half) {
+      const bool low = j < rot_half;
+      const uint4 other = src[low ? i + rot_half / 8 : i - rot_half / 8];
+      const __nv_bfloat162* o = reinterpret_cast<const __nv_bfloat162*>(&other);
+      const int a = low ? j : j - rot_half;                      // index of the angle of the word's first pair
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 x = __bfloat1622float2(p[e]), y = __bfloat1622float2(o[e]);
+        const float c0 = turn[a + 2 * e], c1 = turn[a + 2 * e + 1], s0 = turn[rot_half + a + 2 * e], s1 = turn[rot_half + a + 2 * e + 1];
+        const float r0 = low ? x.x * c0 - y.x * s0 : x.x * c0 + y.x * s0;
+        const float r1 = low ? x.y * c1 - y.y * s1 : x.y * c1 + y.y * s1;
+        p[e] = __floats2bfloat162_rn(r0 * by, r1 * by);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(p[e]);
+        p[e] = __floats2bfloat162_rn(f.x * by, f.y * by);
+      }
+    }
+    return raw;
+  };
   if (vec) {
     const uint4* src = reinterpret_cast<const uint4*>(row);
     uint4* dst = reinterpret_cast<uint4*>(q_out + (int64_t)t * wq);
-    for (int i = threadIdx.x; i < wq / 8; i += blockDim.x) {
-      uint4 raw = src[i];
-      if (temp != 1.f) {
-        __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __bfloat1622float2(p[j]);
-          p[j] = __floats2bfloat162_rn(f.x * temp, f.y * temp);
-        }
-      }
-      dst[i] = raw;
-    }
+    for (int i = threadIdx.x; i < wq / 8; i += blockDim.x) dst[i] = turned_word(src, i, temp);
   } else {
     for (int i = threadIdx.x; i < wq; i += blockDim.x) q_out[(int64_t)t * wq + i] = from_f32<T>(turned(row, i) * temp);
   }
@@ -126,7 +144,7 @@ qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict
     const int k8 = dk / 8, v8 = dv / 8;
     for (int i = threadIdx.x; i < wk / 8; i += blockDim.x) {
       const int g = i / k8, c = i % k8;
-      reinterpret_cast<uint4*>(k_cache + ((page * nkv + g) * page_size + offset) * dk)[c] = src[wq / 8 + i];
+      reinterpret_cast<uint4*>(k_cache + ((page * nkv + g) * page_size + offset) * dk)[c] = turned_word(src + wq / 8, i, 1.f);
     }
     for (int i = threadIdx.x; i < wv / 8; i += blockDim.x) {
       const int g = i / v8, c = i % v8;

@@ -862,7 +862,7 @@ def attention_sink(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     window = -chunk if chunk else window            # the kernels take a chunk as a negative window
     common = dict(nq=nq, nkv=nkv, dk=dk, dv=dv, scale=scale, window=window, bias=bias, sink=sink)
     lib = library()
-    tensor_memory = (q.dtype == torch.bfloat16 and dk == dv and nq // nkv <= 16 and not chunk
+    tensor_memory = (q.dtype == torch.bfloat16 and dk == dv and nq // nkv <= 16
                      and lib.vosti_attention_prefill_tc_supported(dk, group.page_size))
     if not tensor_memory or getattr(ctx, "layout", None) is None or "attention" not in ctx.layout:
         _attention_sink_rows(ctx, q, k_cache, v_cache, out, group, token_list=None, count=tokens, **common)
