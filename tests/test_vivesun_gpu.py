@@ -421,6 +421,10 @@ def test_gelu_expert_mixture_against_plain(dtype, experts, top, ff, scale, monke
     assert torch.equal(chosen.cpu().long(), index)
     assert torch.allclose(weights.cpu(), values / values.sum(-1, keepdim=True) * scale, atol=1e-5)
     assert torch.allclose(dense.cpu().sum(-1), torch.full((T,), scale), atol=1e-5)
+    # the product and the choice in one kernel
+    fused = ops.moe_router(x.to(DEV, dtype), W["router"].to(DEV), top, over_all=True, scale=scale, want_logits=True)
+    assert torch.equal(fused[0].cpu().long(), index) and torch.allclose(fused[3].cpu(), logits, atol=1e-4)
+    assert torch.allclose(fused[1].cpu(), weights.cpu(), atol=1e-5) and torch.allclose(fused[2].cpu(), dense.cpu(), atol=1e-5)
 
 
 def test_branch_sum():

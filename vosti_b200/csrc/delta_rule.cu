@@ -144,7 +144,7 @@ delta_conv_kernel(const void* proj, int proj_f32, int stride, int off_q, int cc,
   const int start = cu_q[b], n = cu_q[b + 1] - start;
   float* tail = state + (int64_t)slot * state_stride + conv_offset;
   const int keep = taps - 1;
-  for (int c = threadIdx.x; c < cc; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < cc; c += gridDim.y * blockDim.x) {
     float next[MAX_TAPS];
     for (int r = 0; r < keep; ++r) {
       const int idx = n + r;                 // row of [old tail (keep rows) ; projection rows (n)]
@@ -356,16 +356,16 @@ struct GeneralPrepArgs {
   float* r; float* k; float* v; float* decay; float* unit; float* removal; float* gate;
 };
 
-// One block per token, one warp per head at a time.
-__global__ void __launch_bounds__(256) general_prep_kernel(GeneralPrepArgs a) {
+// One warp per (token, head): blocks of four warps, blockIdx.y over groups of four heads.
+__global__ void __launch_bounds__(128) general_prep_kernel(GeneralPrepArgs a) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t row = (int64_t)t * a.stride;
   const int hd = a.heads * a.d;
   const float rate = 0.6065306597126334f;             // exp(-1/2)
-  for (int head = warp; head < a.heads; head += nwarps) {
+  for (int head = blockIdx.y * 4 + warp; head < a.heads; head += gridDim.y * 4) {
     const int c0 = head * a.d;
     float ss = 0.f;
     for (int i = lane; i < a.d; i += 32) {
@@ -569,7 +569,7 @@ VOSTI_API int vosti_delta_prep(const void* proj, int proj_f32, int stride, int o
   if (e != cudaSuccess) { vosti_set_error("%s", cudaGetErrorString(e)); return (int)e; }
   // the tail is rewritten only after every token of the step has read the old one
   if (taps > 1)
-    vosti_launch(delta_conv_kernel, dim3(requests), dim3(256), 0, stream, proj, proj_f32, stride, off_q, cc, taps, state,
+    vosti_launch(delta_conv_kernel, dim3(requests, (cc + 255) / 256 < 64 ? (cc + 255) / 256 : 64), dim3(256), 0, stream, proj, proj_f32, stride, off_q, cc, taps, state,
                  state_stride, conv_offset, cu_q, state_slots, num_slots);
   VOSTI_LAUNCH_CHECK();
 }
@@ -656,7 +656,8 @@ VOSTI_API int vosti_general_delta_prep(const void* proj, int proj_f32, int strid
   a.off_r = off_r; a.off_k = off_k; a.off_v = off_v; a.off_g = off_g; a.off_a = off_a;
   a.inner = inner; a.w0 = w0; a.a_bias = a_bias; a.w_f32 = w_f32; a.heads = heads; a.d = d;
   a.r = r; a.k = k; a.v = v; a.decay = decay; a.unit = unit; a.removal = removal; a.gate = gate;
-  vosti_launch(general_prep_kernel, dim3(tokens), dim3(256), 0, stream, a);
+  VOSTI_REQUIRE((heads + 3) / 4 <= 65535, "general_delta_prep: too many heads");
+  vosti_launch(general_prep_kernel, dim3(tokens, (heads + 3) / 4), dim3(128), 0, stream, a);
   VOSTI_LAUNCH_CHECK();
 }
 

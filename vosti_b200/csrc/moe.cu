@@ -22,15 +22,10 @@
 
 namespace {
 
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, int tokens, int experts, int top, int* __restrict__ chosen,
-                 float* __restrict__ weights, float* __restrict__ dense, int over_all, float scale) {
-  pdl_wait();
-  pdl_launch_dependents();
+// One warp: the choice for token t from its row of logits (global or shared memory).
+__device__ __forceinline__ void route_row(const float* row, int t, int experts, int top, int* __restrict__ chosen,
+                                          float* __restrict__ weights, float* __restrict__ dense, int over_all, float scale) {
   const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (t >= tokens) return;
-  const float* row = logits + (int64_t)t * experts;
   for (int e = lane; e < experts; e += 32) dense[(int64_t)t * experts + e] = 0.f;
   float first = 0.f, total = 0.f;
   unsigned long long taken_low = 0;     // experts 0..63 this lane already gave away (bit e / 32 of its share)
@@ -72,6 +67,46 @@ moe_route_kernel(const float* __restrict__ logits, int tokens, int experts, int 
       weights[(int64_t)t * top + r] = w;
       dense[(int64_t)t * experts + chosen[(int64_t)t * top + r]] = w;
     }
+}
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int tokens, int experts, int top, int* __restrict__ chosen,
+                 float* __restrict__ weights, float* __restrict__ dense, int over_all, float scale) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  route_row(logits + (int64_t)t * experts, t, experts, top, chosen, weights, dense, over_all, scale);
+}
+
+// The router's product and the choice in one kernel, one block per token: the token's row goes to
+// shared memory as float32, every warp makes the logits of its experts (a lane's multiply-add
+// chain over k = lane, lane + 32, ..., then the warp's fixed tree: the order depends on k alone),
+// and the first warp chooses. The router's matrix is float32 [experts, k].
+__global__ void __launch_bounds__(128)
+moe_router_kernel(const void* __restrict__ x, int x_f32, const float* __restrict__ router, int experts, int k, int top,
+                  int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ dense, float* __restrict__ logits,
+                  int over_all, float scale) {
+  extern __shared__ float router_smem[];         // [k] the token's row, then [experts] its logits
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* xs = router_smem;
+  float* lg = router_smem + k;
+  for (int i = threadIdx.x; i < k; i += blockDim.x) xs[i] = load_flex(x, x_f32, (int64_t)t * k + i);
+  __syncthreads();
+  for (int e = warp; e < experts; e += 4) {
+    const float* w = router + (int64_t)e * k;
+    float acc = 0.f;
+    for (int i = lane; i < k; i += 32) acc = fmaf(xs[i], w[i], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      lg[e] = acc;
+      if (logits != nullptr) logits[(int64_t)t * experts + e] = acc;
+    }
+  }
+  __syncthreads();
+  if (warp == 0) route_row(lg, t, experts, top, chosen, weights, dense, over_all, scale);
 }
 
 // `dense` null: the activation alone.
@@ -181,5 +216,27 @@ VOSTI_API int vosti_moe_scale(void* act, const float* dense, int tokens, int exp
   const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
   if (is_f32) vosti_launch(moe_scale_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)act, dense, (int64_t)tokens, experts, ff, gelu);
   else vosti_launch(moe_scale_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)act, dense, (int64_t)tokens, experts, ff, gelu);
+  VOSTI_LAUNCH_CHECK();
+}
+
+// x [tokens, k] float32 or bfloat16; router float32 [experts, k]; `logits` (optional) receives the
+// float32 logits [tokens, experts].
+VOSTI_API int vosti_moe_router(const void* x, int x_f32, const float* router, int tokens, int experts, int k, int top,
+                               int* chosen, float* weights, float* dense, float* logits, int over_all, float scale,
+                               cudaStream_t stream) {
+  VOSTI_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && top <= experts && k > 0, "moe_router: bad sizes experts=%d top=%d", experts, top);
+  VOSTI_REQUIRE(experts <= 2048, "moe_router: %d experts (at most 2048 are taken)", experts);
+  const size_t smem = (size_t)(k + experts) * sizeof(float);
+  VOSTI_REQUIRE(smem <= 200 * 1024, "moe_router: a row of %d elements does not fit shared memory", k);
+  if (tokens == 0) return VOSTI_OK;
+  {
+    static bool configured = false;       // once, to the most a launch may ask for
+    if (!configured) {
+      cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      configured = true;
+    }
+  }
+  vosti_launch(moe_router_kernel, dim3(tokens), dim3(128), smem, stream, x, x_f32, router, experts, k, top, chosen, weights,
+               dense, logits, over_all, scale);
   VOSTI_LAUNCH_CHECK();
 }

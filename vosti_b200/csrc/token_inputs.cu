@@ -55,6 +55,25 @@ pair_embedding_kernel(const int* __restrict__ ids, const int* __restrict__ sourc
   const T* a = table + (int64_t)id * hidden;
   const T* p = pairs + row * hidden;
   float* dst = out + (int64_t)t * hidden;
+  if (sizeof(T) == 2 && hidden % 8 == 0 && !bad) {          // 16-byte words of bfloat16
+    const uint4* a8 = reinterpret_cast<const uint4*>(a);
+    const uint4* p8 = reinterpret_cast<const uint4*>(p);
+    for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) {
+      const uint4 ra = a8[i], rp = p8[i];
+      const __nv_bfloat162* xa = reinterpret_cast<const __nv_bfloat162*>(&ra);
+      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&rp);
+      float r[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 fa = __bfloat1622float2(xa[e]), fp = __bfloat1622float2(xp[e]);
+        r[2 * e] = fa.x + fp.x;
+        r[2 * e + 1] = fa.y + fp.y;
+      }
+      reinterpret_cast<float4*>(dst)[2 * i] = make_float4(r[0], r[1], r[2], r[3]);
+      reinterpret_cast<float4*>(dst)[2 * i + 1] = make_float4(r[4], r[5], r[6], r[7]);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = bad ? 0.f : to_f32(a[i]) + to_f32(p[i]);
 }
 

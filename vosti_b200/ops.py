@@ -1001,6 +1001,24 @@ def moe_route(logits: torch.Tensor, top: int, *, over_all: bool = False, scale: 
     return chosen, weights, dense
 
 
+def moe_router(x: torch.Tensor, router: torch.Tensor, top: int, *, over_all: bool = False, scale: float = 1.0,
+               want_logits: bool = False):
+    """The router's product x @ router.T (float32 arithmetic, router float32 [experts, k]) and
+    `moe_route` of it in one kernel: (chosen, weights, dense), and the logits too if asked for."""
+    x = materialize(x)
+    _contig(x, router)
+    if router.dtype != torch.float32 or router.shape[1] != x.shape[1]:
+        raise KernelError("moe_router: the router is float32 [experts, k]")
+    tokens, experts = x.shape[0], router.shape[0]
+    chosen = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=x.device)
+    dense = torch.empty((tokens, experts), dtype=torch.float32, device=x.device)
+    logits = torch.empty((tokens, experts), dtype=torch.float32, device=x.device) if want_logits else None
+    _check(library().vosti_moe_router(_p(x), _is_f32(x), _p(router), tokens, experts, x.shape[1], top, _p(chosen), _p(weights),
+                                      _p(dense), _p(logits), int(over_all), ctypes.c_float(scale), _stream()), "moe_router")
+    return (chosen, weights, dense, logits) if want_logits else (chosen, weights, dense)
+
+
 def moe_scale(act: torch.Tensor, dense: Optional[torch.Tensor], ff: int, *, gelu: bool = False) -> torch.Tensor:
     """act[t, e * ff + i] <- f(act[t, e * ff + i]) * dense[t, e], in place; f is the exact GELU with
     `gelu`, else the identity; without `dense` the activation alone."""

@@ -173,8 +173,7 @@ class ExpertMixture(FeedForward):
 
     def forward(self, ctx, x):
         x = ops.materialize(x)
-        logits = ops.gemm_simt(x, self.router, ctx.status, out_dtype=torch.float32)
-        chosen, weights, dense = ops.moe_route(logits, self.top, over_all=self.route == "softmax_renorm", scale=self.scale)
+        chosen, weights, dense = ops.moe_router(x, self.router, self.top, over_all=self.route == "softmax_renorm", scale=self.scale)
         if (self.per_expert and x.shape[0] >= self.GROUPED_FROM and not getattr(ctx, "all_decode", True)
                 and not torch.cuda.is_current_stream_capturing()):
             out = self._grouped(ctx, x, chosen, weights)
