@@ -198,7 +198,7 @@ def run_attention(mixer, harness, qkv, sizes, dtype, rid="r"):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv,dk,dv,chunk,rot,page", [(4, 2, 24, 16, 7, 24, 8), (2, 1, 16, 40, 20, 2, 8), (3, 3, 8, 8, 1, 4, 4),
+@pytest.mark.parametrize("heads,kv,dk,dv,chunk,rot,page", [(4, 2, 24, 16, 7, 24, 8), (2, 1, 16, 40, 20, 2, 8), (3, 3, 8, 8, 1, 4, 4), (2, 1, 6, 10, 5, 6, 4),
                                                           (4, 2, 64, 64, 48, 32, 16), (2, 2, 128, 128, 100, 64, 16),
                                                           (6, 1, 64, 64, 33, 16, 16)])
 def test_rotated_chunked_attention_against_plain(dtype, heads, kv, dk, dv, chunk, rot, page):
@@ -303,7 +303,7 @@ def run_mixer(mixer, harness, x, sizes, dtype, rid="r"):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,d,rank", [(3, 20, 3), (2, 40, 2), (1, 48, 5), (2, 64, 16), (6, 8, 1), (1, 130, 4)])
+@pytest.mark.parametrize("heads,d,rank", [(3, 20, 3), (2, 40, 2), (1, 48, 5), (2, 64, 16), (6, 8, 1), (1, 130, 4), (2, 5, 2)])
 def test_general_delta_rule_against_plain(dtype, heads, d, rank):
     gen = torch.Generator().manual_seed(heads * 10 + d)
     width, T, eps = 72, 50, 1e-5
@@ -345,7 +345,8 @@ def test_general_delta_recurrence_kernel_alone_with_strong_removal():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv,dk,dv,taps", [(4, 2, 8, 12, 2), (3, 3, 40, 20, 4), (1, 1, 48, 48, 1), (4, 2, 64, 64, 4), (2, 1, 16, 70, 5)])
+@pytest.mark.parametrize("heads,kv,dk,dv,taps", [(4, 2, 8, 12, 2), (3, 3, 40, 20, 4), (1, 1, 48, 48, 1), (4, 2, 64, 64, 4), (2, 1, 16, 70, 5),
+                                                 (2, 1, 5, 3, 3)])
 def test_gated_delta_rule_with_a_decay_per_head_against_plain(dtype, heads, kv, dk, dv, taps):
     gen = torch.Generator().manual_seed(heads * 10 + dk)
     width, T, eps = 72, 50, 1e-5
@@ -460,7 +461,7 @@ def close_rows(got, want, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_whole_prompt_portions_and_decoding_against_plain(models, name, dtype, monkeypatch):
     from vosti_b200.parts import ExpertMixture
     monkeypatch.setattr(ExpertMixture, "GROUPED_FROM", 16)      # portions of 16 tokens or more sort their pairs by expert
@@ -500,7 +501,7 @@ def test_residual_stream_after_every_layer(models):
         assert torch.allclose(got, expected, atol=2e-4, rtol=2e-4)
 
 
-@pytest.mark.parametrize("name,dtype", [("a", "float32"), ("b", "float32"), ("c", "float32"), ("c", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [("a", "float32"), ("b", "float32"), ("c", "float32"), ("c", "bfloat16"), ("d", "float32")])
 def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(models, name, dtype):
     """Four requests through two state slots and a pool that holds two of them: portions of some
     beside single tokens of others; every request equals itself alone."""

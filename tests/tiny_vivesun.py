@@ -9,6 +9,8 @@ A: odd sizes everywhere; parallel and delta layers alternating, a parallel layer
 B: no per-layer token input; one expert; a convolution of one tap (no tail in the state); one
    head; a chunk of one position (a query sees itself only); a key width that needs two lanes per
    column in the recurrences.
+D: gated-delta layers only (no paged cache at all), sizes that are no multiple of 4, one layer
+   without a feed-forward, a token input of one element.
 C: attention heads of 64 with equal key and value widths and pages of 16 tokens (the sizes that
    the tensor-core attention kernels take in bfloat16); two parallel layers sharing a page group.
 """
@@ -66,8 +68,13 @@ C = dict(architecture="Vivesun", vocab=160, width=128, norm=dict(eps=1e-6), toke
     _delta(4, 2, 24, 32, 3, _moe(4, 2, 32, 1.0)),
     _parallel(_left(2, 2, 64, 64, 0.125, 33, _rot(50000.0, 64)), 2, 16, 1.1, 0.4, None),
 ])
-ALL = {"a": (A, 3, 21), "b": (B, 2, 22), "c": (C, 8, 23)}      # config, rank of the decay pair, seed
-PAGE = {"a": 8, "b": 8, "c": 16}
+D = dict(architecture="Vivesun", vocab=67, width=50, norm=dict(eps=1e-5), token_side=dict(dim=1),
+         embedding=dict(bigram=dict(buckets=5, mul_prev=3, mul_cur=2)), layers=[
+    _delta(2, 1, 5, 3, 3, _moe(3, 2, 7, 1.0)),
+    _delta(3, 3, 6, 9, 2, None),
+])
+ALL = {"a": (A, 3, 21), "b": (B, 2, 22), "c": (C, 8, 23), "d": (D, 1, 24)}      # config, rank of the decay pair, seed
+PAGE = {"a": 8, "b": 8, "c": 16, "d": 4}
 
 
 def draw(name, shape, gen):
