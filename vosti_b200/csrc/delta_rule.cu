@@ -14,7 +14,7 @@
 // channels a lane keeps are contiguous, then the convolution tail [taps - 1, conv channels].
 //
 // Kernels:
-//   delta_prep     one block per token: convolutions, unit vectors, beta, decay, gate
+//   delta_prep     one warp per (token, q / k / v head): convolutions, unit vectors; beta, decay, gate
 //   delta_conv     one block per request: the convolution tail after this step
 //   delta_scan     one block per (request, head, block of value columns): the recurrence over
 //                  the request's tokens of this step, from and to the state slot. Columns of S
@@ -72,24 +72,27 @@ struct PrepArgs {
   int gate_silu;                // the output gate is z * sigmoid(z) instead of sigmoid(z)
 };
 
+// One warp per unit of a token: a q head, a k head or a v head. A lane owns the channels lane,
+// lane + 32, ... of its unit, convolves them, and for q and k heads the warp sums the squares
+// (a lane's chain, then the fixed tree). blockIdx.y walks the units in groups of the block's
+// warps; the element-wise outputs (beta, decay, gate) are spread over the same blocks.
+constexpr int PREP_MAX_KEY = 256;            // widest q / k head (8 channels per lane)
 __global__ void __launch_bounds__(256) delta_prep_kernel(PrepArgs a) {
-  extern __shared__ float smem[];
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const int cq = a.kv_heads * a.dk, cv = a.heads * a.dv, cc = 2 * cq + cv;
-  float* y = smem;                        // [cc] convolved and activated q | k | v
   const int b = a.request_of[t];
   const int local = t - a.cu_q[b];
   int slot = a.state_slots[b];
   if (slot < 0 || slot >= a.num_slots) {
-    if (threadIdx.x == 0) raise_fault(a.status, VOSTI_FAULT_SLOT_RANGE);
+    if (threadIdx.x == 0 && blockIdx.y == 0) raise_fault(a.status, VOSTI_FAULT_SLOT_RANGE);
     slot = 0;
   }
   const float* tail = a.state + (int64_t)slot * a.state_stride + a.conv_offset;   // [taps - 1, cc]
   const int64_t row = (int64_t)t * a.stride;
   // q | k | v occupy columns off_q .. off_q + cc of the projection in this order
-  for (int c = threadIdx.x; c < cc; c += blockDim.x) {
+  auto convolved = [&](int c) {
     float acc = 0.f;
     for (int i = 0; i < a.taps; ++i) {
       const int back = a.taps - 1 - i;                  // how many tokens before this one
@@ -98,34 +101,48 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(PrepArgs a) {
       else x = tail[(int64_t)(a.taps - 1 + local - back) * cc + c];
       acc = fmaf(load_flex(a.conv_w, a.w_f32, (int64_t)c * a.taps + i), x, acc);
     }
-    y[c] = acc * sigmoidf_(acc);
-  }
-  __syncthreads();
+    return acc * sigmoidf_(acc);
+  };
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  // unit vectors: one warp per q or k head
-  for (int head = warp; head < 2 * a.kv_heads; head += nwarps) {
-    const float* src = y + head * a.dk;
-    float ss = 0.f;
-    for (int i = lane; i < a.dk; i += 32) ss += src[i] * src[i];
-    ss = warp_sum(ss);
-    const bool is_q = head < a.kv_heads;
-    const float scale = (1.f / sqrtf(ss + 1e-6f)) * (is_q ? 1.f / sqrtf((float)a.dk) : 1.f);
-    float* dst = (is_q ? a.q : a.k) + (int64_t)t * cq + (is_q ? head : head - a.kv_heads) * a.dk;
-    for (int i = lane; i < a.dk; i += 32) dst[i] = src[i] * scale;
+  const int units = 2 * a.kv_heads + a.heads;
+  for (int unit = blockIdx.y * nwarps + warp; unit < units; unit += gridDim.y * nwarps) {
+    if (unit < 2 * a.kv_heads) {
+      const int c0 = unit * a.dk;                       // q heads, then k heads
+      float y[PREP_MAX_KEY / 32];
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < PREP_MAX_KEY / 32; ++j) {
+        const int i = lane + 32 * j;
+        y[j] = i < a.dk ? convolved(c0 + i) : 0.f;
+        ss += y[j] * y[j];
+      }
+      ss = warp_sum(ss);
+      const bool is_q = unit < a.kv_heads;
+      const float scale = (1.f / sqrtf(ss + 1e-6f)) * (is_q ? 1.f / sqrtf((float)a.dk) : 1.f);
+      float* dst = (is_q ? a.q : a.k) + (int64_t)t * cq + (is_q ? unit : unit - a.kv_heads) * a.dk;
+#pragma unroll
+      for (int j = 0; j < PREP_MAX_KEY / 32; ++j) {
+        const int i = lane + 32 * j;
+        if (i < a.dk) dst[i] = y[j] * scale;
+      }
+    } else {
+      const int c0 = (unit - 2 * a.kv_heads) * a.dv;
+      for (int i = lane; i < a.dv; i += 32) a.v[(int64_t)t * cv + c0 + i] = convolved(2 * cq + c0 + i);
+    }
   }
-  for (int c = threadIdx.x; c < cv; c += blockDim.x) a.v[(int64_t)t * cv + c] = y[2 * cq + c];
-  for (int h = threadIdx.x; h < a.heads; h += blockDim.x)
+  const int first = blockIdx.y * blockDim.x + threadIdx.x, step = gridDim.y * blockDim.x;
+  for (int h = first; h < a.heads; h += step)
     a.beta[(int64_t)t * a.heads + h] = sigmoidf_(load_flex(a.proj, a.proj_f32, row + a.off_beta + h));
   const int cd = a.heads * a.dk;
   const int rd = a.decay_per_head ? a.heads : cd;           // decay columns of the rates
   const int64_t rrow = (int64_t)t * (rd + cv);
-  for (int c = threadIdx.x; c < cd; c += blockDim.x) {
+  for (int c = first; c < cd; c += step) {
     const int from = a.decay_per_head ? c / a.dk : c;
     const float rate = load_flex(a.rates, a.rates_f32, rrow + from) + load_flex(a.dt_bias, a.w_f32, from);
     const float speed = expf(load_flex(a.a_log, a.w_f32, c / a.dk));
     a.decay[(int64_t)t * cd + c] = expf(-speed * softplusf_(rate));
   }
-  for (int c = threadIdx.x; c < cv; c += blockDim.x) {
+  for (int c = first; c < cv; c += step) {
     const float z = load_flex(a.rates, a.rates_f32, rrow + rd + c);
     a.gate[(int64_t)t * cv + c] = a.gate_silu ? z * sigmoidf_(z) : sigmoidf_(z);
   }
@@ -554,17 +571,9 @@ VOSTI_API int vosti_delta_prep(const void* proj, int proj_f32, int stride, int o
   a.q = q; a.k = k; a.v = v; a.beta = beta; a.decay = decay; a.gate = gate; a.status = status;
   a.decay_per_head = decay_per_head; a.gate_silu = gate_silu;
   const int cc = 2 * kv_heads * dk + heads * dv;
-  const size_t smem = (size_t)cc * sizeof(float);
-  VOSTI_REQUIRE(smem <= 200 * 1024, "delta_prep: %d channels do not fit shared memory", cc);
-  {
-    // once, to the most a launch may ask for: the attribute is not touched while launches are in flight
-    static bool configured = false;
-    if (!configured) {
-      cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-      configured = true;
-    }
-  }
-  vosti_launch(delta_prep_kernel, dim3(tokens), dim3(256), smem, stream, a);
+  VOSTI_REQUIRE(dk <= PREP_MAX_KEY, "delta_prep: %d key channels (at most %d are taken)", dk, PREP_MAX_KEY);
+  const int units = 2 * kv_heads + heads;
+  vosti_launch(delta_prep_kernel, dim3(tokens, (units + 7) / 8 < 65535 ? (units + 7) / 8 : 65535), dim3(256), 0, stream, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { vosti_set_error("%s", cudaGetErrorString(e)); return (int)e; }
   // the tail is rewritten only after every token of the step has read the old one

@@ -83,11 +83,11 @@ moe_route_kernel(const float* __restrict__ logits, int tokens, int experts, int 
 // shared memory as float32, every warp makes the logits of its experts (a lane's multiply-add
 // chain over k = lane, lane + 32, ..., then the warp's fixed tree: the order depends on k alone),
 // and the first warp chooses. The router's matrix is float32 [experts, k].
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_router_kernel(const void* __restrict__ x, int x_f32, const float* __restrict__ router, int experts, int k, int top,
                   int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ dense, float* __restrict__ logits,
                   int over_all, float scale) {
-  extern __shared__ float router_smem[];         // [k] the token's row, then [experts] its logits
+  extern __shared__ __align__(16) float router_smem[];         // [k] the token's row, then [experts] its logits
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -95,10 +95,27 @@ moe_router_kernel(const void* __restrict__ x, int x_f32, const float* __restrict
   float* lg = router_smem + k;
   for (int i = threadIdx.x; i < k; i += blockDim.x) xs[i] = load_flex(x, x_f32, (int64_t)t * k + i);
   __syncthreads();
-  for (int e = warp; e < experts; e += 4) {
+  const int nwarps = blockDim.x >> 5;
+  for (int e = warp; e < experts; e += nwarps) {
     const float* w = router + (int64_t)e * k;
     float acc = 0.f;
-    for (int i = lane; i < k; i += 32) acc = fmaf(xs[i], w[i], acc);
+    if (k % 4 == 0) {
+      // 16-byte words, four of them in flight: a lane's chain runs over the words lane, lane + 32, ...
+      float part[4] = {0.f, 0.f, 0.f, 0.f};
+      const float4* w4 = reinterpret_cast<const float4*>(w);
+      const float4* x4 = reinterpret_cast<const float4*>(xs);
+#pragma unroll 4
+      for (int i = lane; i < k / 4; i += 32) {
+        const float4 a = x4[i], b = w4[i];
+        part[0] = fmaf(a.x, b.x, part[0]);
+        part[1] = fmaf(a.y, b.y, part[1]);
+        part[2] = fmaf(a.z, b.z, part[2]);
+        part[3] = fmaf(a.w, b.w, part[3]);
+      }
+      acc = (part[0] + part[1]) + (part[2] + part[3]);
+    } else {
+      for (int i = lane; i < k; i += 32) acc = fmaf(xs[i], w[i], acc);
+    }
     acc = warp_sum(acc);
     if (lane == 0) {
       lg[e] = acc;
@@ -236,7 +253,7 @@ VOSTI_API int vosti_moe_router(const void* x, int x_f32, const float* router, in
       configured = true;
     }
   }
-  vosti_launch(moe_router_kernel, dim3(tokens), dim3(128), smem, stream, x, x_f32, router, experts, k, top, chosen, weights,
+  vosti_launch(moe_router_kernel, dim3(tokens), dim3(experts > 4 ? 256 : 128), smem, stream, x, x_f32, router, experts, k, top, chosen, weights,
                dense, logits, over_all, scale);
   VOSTI_LAUNCH_CHECK();
 }
