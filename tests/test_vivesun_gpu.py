@@ -150,7 +150,7 @@ def test_token_input_against_plain(dtype):
 
 def test_rotation_frequencies_follow_the_wavelength_rule():
     from vosti_b200.parts import build_position
-    for dims, base, scaling in ((16, 250000.0, (8.0, 1.0, 4.0, 2048)), (24, 100.0, (4.0, 1.0, 3.0, 40)), (8, 10000.0, None),
+    for dims, base, scaling in ((16, 300000.0, (6.0, 1.0, 4.0, 4096)), (24, 100.0, (4.0, 1.0, 3.0, 40)), (8, 10000.0, None),
                                 (6, 50.0, (2.0, 0.5, 2.0, 16))):
         part = build_position(PartSpec.make("rope", theta=base, rotary_dim=dims, max_positions=0,
                                             scaling=None if scaling is None else ("wavelength",) + scaling), 64, 64)
