@@ -386,10 +386,10 @@ def vivesun_config(size):
     left = dict(heads=size["heads"], kv_heads=size["kv"], dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=1024),
                 rot=dict(base=500000.0, dims=64, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
     parallel = dict(type="parallel", mlp=mlp, mixer=dict(left=left, right=dict(heads=size["heads"], dim=128),
-                                                         left_scale=0.8, right_scale=0.9))
+                                                         left_scale=1.0, right_scale=1.0))
     delta = dict(type="delta", mlp=mlp, mixer=dict(heads=size["heads"], kv_heads=size["kv"], dim=128, vdim=128, conv=4))
     config = dict(architecture="Vivesun", vocab=size["vocab"], width=size["width"], norm=dict(eps=1e-6), token_side=dict(dim=64),
-                  embedding=dict(bigram=dict(buckets=65521, mul_prev=127, mul_cur=7)),
+                  embedding=dict(bigram=dict(buckets=65521, mul_prev=1000003, mul_cur=31)),
                   layers=[delta if i % 2 == 0 else parallel for i in range(size["layers"])])
     return config, checkpoint_shapes(config, decay_rank=64)
 

@@ -64,7 +64,7 @@ B = dict(architecture="Vivesun", vocab=128, width=64, norm=dict(eps=1e-5), token
 ])
 C = dict(architecture="Vivesun", vocab=160, width=128, norm=dict(eps=1e-6), token_side=dict(dim=8),
          embedding=dict(bigram=dict(buckets=509, mul_prev=31, mul_cur=17)), layers=[
-    _parallel(_left(4, 2, 64, 64, 0.125, 48, _rot(10000.0, 32, _scaling(8.0, 1.0, 4.0, 64))), 2, 32, 0.8, 0.9, _moe(4, 2, 32, 2.0)),
+    _parallel(_left(4, 2, 64, 64, 0.125, 48, _rot(10000.0, 32, _scaling(8.0, 1.0, 4.0, 64))), 2, 32, 0.7, 1.3, _moe(4, 2, 32, 2.5)),
     _delta(4, 2, 24, 32, 3, _moe(4, 2, 32, 1.0)),
     _parallel(_left(2, 2, 64, 64, 0.125, 33, _rot(50000.0, 64)), 2, 16, 1.1, 0.4, None),
 ])
