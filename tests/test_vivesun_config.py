@@ -76,19 +76,34 @@ def test_the_rank_comes_from_the_checkpoint(tmp_path):
     (lambda c: c["norm"].pop("eps"), "lacks 'eps'"),
     (lambda c: c["layers"][0].update(type="window"), "'delta' and 'parallel' are known"),
     (lambda c: c["layers"][0]["mixer"]["left"]["mask"].update(size=0), "positive integer"),
-    (lambda c: c["layers"][0]["mixer"]["left"]["rot"].pop("scaling"), "lacks 'scaling'"),
+    (lambda c: c["layers"][0]["mixer"]["left"]["rot"].pop("base"), "lacks 'base'"),
     (lambda c: c["layers"][0]["mixer"].pop("right_scale"), "lacks 'right_scale'"),
     (lambda c: c["layers"][0]["mlp"].update(kind="dense"), "'moe' is known"),
-    (lambda c: c["layers"][0]["mlp"]["router"].pop("scale"), "lacks 'scale'"),
+    (lambda c: c["layers"][0]["mlp"]["router"].pop("top"), "lacks 'top'"),
     (lambda c: c["layers"][1]["mixer"].pop("conv"), "lacks 'conv'"),
     (lambda c: c["embedding"]["bigram"].update(buckets=-3), "positive integer"),
-    (lambda c: c.pop("token_side"), "lacks 'token_side'"),
+    (lambda c: c["token_side"].pop("dim"), "lacks 'dim'"),
 ])
 def test_missing_or_bad_keys_are_errors(damage, message):
     config = copy.deepcopy(tiny.A)
     damage(config)
     with pytest.raises(ConfigError, match=message):
         spec_of(config, 3)
+
+
+def test_optional_blocks_may_be_absent():
+    config = copy.deepcopy(tiny.A)
+    config.pop("token_side")
+    config["layers"][0].pop("mlp")
+    config["layers"][0]["mixer"]["left"].pop("mask")
+    config["layers"][0]["mixer"]["left"]["rot"].pop("scaling")
+    config["layers"][2]["mlp"]["router"].pop("scale")
+    spec = spec_of(config, 3)
+    left = dict(spec.layers[0].mixer["branches"])["left"]
+    assert left["chunk"] == 0 and left["position"]["scaling"] is None
+    assert spec.layers[0].feed_forward is None and spec.layers[0].token_input is None
+    assert spec.layers[2].feed_forward["scale"] == 1.0
+    assert "side.embed" not in expected_weights(spec)
 
 
 def test_part_parameters_are_checked():

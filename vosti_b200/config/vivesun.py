@@ -13,20 +13,22 @@ embedding table. Two kinds of layer, in any order:
               own chunk of positions only, one added to the softmax denominator) and a generalized
               delta rule with a decay and a removal rate per (head, key channel).
 
-Keys (a missing one is an error; nothing has a default):
+Keys (a missing one is an error, except the blocks marked "optional", which may be absent or
+null and then switch their mechanism off):
 
     architecture  "Vivesun"
     vocab, width
     norm.eps                       epsilon of every root-mean-square division
     embedding.bigram               buckets, mul_prev, mul_cur
-    token_side                     null | {dim}
+    token_side                     optional: {dim}
     layers[i].type                 "delta" | "parallel"
     layers[i].mixer   (delta)      heads, kv_heads, dim, vdim, conv
     layers[i].mixer   (parallel)   left_scale, right_scale,
-                                   left: heads, kv_heads, dim, vdim, scale, mask.size,
-                                         rot.base, rot.dims, rot.scaling (null | factor, low, high, original)
+                                   left: heads, kv_heads, dim, vdim, scale, mask (optional: size),
+                                         rot.base, rot.dims, rot.scaling (optional: factor, low, high, original)
                                    right: heads, dim
-    layers[i].mlp                  null | {kind: "moe", expert.ff, router.experts, router.top, router.scale}
+    layers[i].mlp                  optional: {kind: "moe", expert.ff, router.experts, router.top,
+                                   router.scale (optional: 1)}
 
 The rank of the generalized rule's decay pair is the first extent of `l<i>.mix.right.w1` in the
 checkpoint (`shapes`).
@@ -77,7 +79,7 @@ def _delta(i: int, block: Mapping[str, Any], eps: float) -> PartSpec:
 
 
 def _rotation(rot: Mapping[str, Any], where: str) -> PartSpec:
-    scaling = _need(rot, "scaling", where)
+    scaling = rot.get("scaling")
     if scaling is not None:
         sw = where + ".scaling"
         scaling = ("wavelength", _number(scaling, "factor", sw), _number(scaling, "low", sw), _number(scaling, "high", sw),
@@ -93,7 +95,8 @@ def _parallel(i: int, block: Mapping[str, Any], eps: float, shapes) -> PartSpec:
     attention = PartSpec.make(
         "sink_attention", num_heads=_positive_int(left, "heads", lw), num_kv_heads=_positive_int(left, "kv_heads", lw),
         head_dim=_positive_int(left, "dim", lw), v_head_dim=_positive_int(left, "vdim", lw),
-        scale=_number(left, "scale", lw), window=0, chunk=_positive_int(_need(left, "mask", lw), "size", lw + ".mask"),
+        scale=_number(left, "scale", lw), window=0,
+        chunk=0 if left.get("mask") is None else _positive_int(left["mask"], "size", lw + ".mask"),
         sink=False, sink_value=0.0, position=_rotation(_need(left, "rot", lw), lw + ".rot"))
     general = PartSpec.make(
         "general_delta", num_heads=_positive_int(right, "heads", rw), head_dim=_positive_int(right, "dim", rw), eps=eps,
@@ -113,7 +116,8 @@ def _feed_forward(i: int, block: Optional[Mapping[str, Any]]) -> Optional[PartSp
     return PartSpec.make("moe", experts=_positive_int(router, "experts", where + ".router"),
                          top=_positive_int(router, "top", where + ".router"),
                          intermediate_size=_positive_int(_need(block, "expert", where), "ff", where + ".expert"),
-                         gated=False, route="softmax_renorm", scale=_number(router, "scale", where + ".router"),
+                         gated=False, route="softmax_renorm",
+                         scale=_number(router, "scale", where + ".router") if "scale" in router else 1.0,
                          float32_out=True)
 
 
@@ -124,7 +128,7 @@ def spec_from_config(raw: Mapping[str, Any], shapes: Optional[Mapping[str, tuple
     eps = _number(_need(raw, "norm", "config"), "eps", "norm")
     norm = PartSpec.make("rms_stream", eps=eps, unit_offset=True)
     pairs = _need(_need(raw, "embedding", "config"), "bigram", "embedding")
-    side = _need(raw, "token_side", "config")
+    side = raw.get("token_side")
     side_dim = 0 if side is None else _positive_int(side, "dim", "token_side")
     layers = _need(raw, "layers", "config")
     if not isinstance(layers, list) or not layers:
@@ -141,7 +145,7 @@ def spec_from_config(raw: Mapping[str, Any], shapes: Optional[Mapping[str, tuple
         else:
             raise ConfigError(f"Vivesun config: layers[{i}].type is {kind!r}; 'delta' and 'parallel' are known")
         token_input = PartSpec.make("gated_table", dim=side_dim, offset=i * side_dim, eps=eps) if side_dim else None
-        specs.append(LayerSpec(mixer=mixer, feed_forward=_feed_forward(i, _need(layer, "mlp", f"layers[{i}]")), norm=norm,
+        specs.append(LayerSpec(mixer=mixer, feed_forward=_feed_forward(i, layer.get("mlp")), norm=norm,
                                position=None, arrangement="pre_norm_stream", names=names, token_input=token_input))
     embedding = PartSpec.make(
         "pair_hash", buckets=_positive_int(pairs, "buckets", "embedding.bigram"),
