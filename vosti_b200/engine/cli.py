@@ -21,8 +21,8 @@ meaning here, and every one also has a flag (the flag wins):
 
 Added here: --dtype {bfloat16,float32} (VOSTI_DTYPE), --block-size (VOSTI_BLOCK_SIZE, the
 reference's page size is the constant 64), --temperature, --seed, --chunk-size, and
---random-config FILE --random-seed N, which first writes a random-weights model folder to
---model. Prints MODEL_OUTPUT_TOKEN_IDS=[...] or, for a prepared workload, the BENCH and
+--random-config FILE --random-seed N [--random-shapes FILE], which first writes a random-weights
+model folder to --model. Prints MODEL_OUTPUT_TOKEN_IDS=[...] or, for a prepared workload, the BENCH and
 CACHE_STATS lines.
 """
 from __future__ import annotations
@@ -153,6 +153,8 @@ def main(argv: Optional[List[str]] = None) -> int:
                              "(slower decoding); decode: decode steps of up to 64 rows do not depend on the batch")
     parser.add_argument("--random-config", help="config.json to draw a random-weights model from")
     parser.add_argument("--random-seed", type=int, default=0)
+    parser.add_argument("--random-shapes", help="JSON file, tensor name -> shape: the sizes an architecture's config.json "
+                                                 "leaves to the checkpoint (Mugizen, Vivesun)")
     args = parser.parse_args(argv)
 
     if not args.model or not args.model.strip():
@@ -161,7 +163,10 @@ def main(argv: Optional[List[str]] = None) -> int:
         raise SystemExit("VOSTI_MAX_TOKENS must be positive")
     if args.random_config:
         from ..weights import write_random_model
-        write_random_model(args.model, json.loads(Path(args.random_config).read_text()), args.random_seed)
+        shapes = None
+        if args.random_shapes:
+            shapes = {name: tuple(shape) for name, shape in json.loads(Path(args.random_shapes).read_text()).items()}
+        write_random_model(args.model, json.loads(Path(args.random_config).read_text()), args.random_seed, shapes=shapes)
 
     from .engine import Engine
 
